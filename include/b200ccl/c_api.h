@@ -1,0 +1,77 @@
+/* C interface of the library, for callers that cannot use the C++ classes (Python through
+ * ctypes, other runtimes). Every function returns 0 on success and a non-zero code on failure;
+ * b2_last_error() then holds the message of the calling thread's last failure.
+ *
+ * nano-nccl has no C or Python surface (its product is C++ only); this layer is what the
+ * PyTorch package of this project is built on. */
+#pragma once
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b2_comm b2_comm;            /* a Communicator */
+typedef struct b2_bootstrap b2_bootstrap;  /* a TCP rendezvous */
+
+const char* b2_last_error(void);
+const char* b2_version(void);
+
+/* enums mirror b200ccl::DType / RedOp / TransportKind / Algo / Collective */
+int b2_parse_dtype(const char* text, int* out);
+int b2_parse_redop(const char* text, int* out);
+int b2_parse_transport(const char* text, int* out);
+int b2_parse_algo(const char* text, int* out);
+const char* b2_dtype_name(int v);
+const char* b2_redop_name(int v);
+const char* b2_transport_name(int v);
+const char* b2_algo_name(int v);
+double b2_busbw_gbs(int collective, double algbw, int nranks);
+
+typedef struct b2_config {
+    int transport;          /* TransportKind */
+    int algo;               /* Algo */
+    int channels;           /* 0 = default */
+    size_t staging_bytes;   /* 0 = default */
+    double wait_timeout_ms; /* 0 = default */
+    int loopback;           /* 1 = emulate loopback_ranks ranks on devices[0] */
+    int loopback_ranks;
+    int enable_nvls;
+} b2_config;
+void b2_config_default(b2_config* cfg);
+
+int b2_bootstrap_create(const char* addr, int port, int rank, int size, int timeout_ms, b2_bootstrap** out);
+void b2_bootstrap_destroy(b2_bootstrap* bs);
+int b2_bootstrap_barrier(b2_bootstrap* bs);
+int b2_bootstrap_allgather(b2_bootstrap* bs, const void* in, void* out, size_t bytes);
+
+/* Single process owning `ndev` GPUs. */
+int b2_comm_create(const int* devices, int ndev, const b2_config* cfg, b2_comm** out);
+/* One process of a group; the bootstrap must outlive the communicator. */
+int b2_comm_create_bootstrap(b2_bootstrap* bs, const int* devices, int ndev, const b2_config* cfg, b2_comm** out);
+void b2_comm_destroy(b2_comm* comm);
+
+int b2_comm_local_ranks(const b2_comm* comm);
+int b2_comm_global_ranks(const b2_comm* comm);
+int b2_comm_first_rank(const b2_comm* comm);
+int b2_comm_transport(const b2_comm* comm);
+int b2_comm_nvls(const b2_comm* comm);
+/* Copies at most cap-1 bytes of the description; returns the full length. */
+size_t b2_comm_describe(const b2_comm* comm, char* buf, size_t cap);
+int b2_comm_check_async_error(const b2_comm* comm);
+
+/* collective: 0 all_reduce, 1 reduce_scatter, 2 all_gather. Arrays have one entry per local
+ * rank; streams are cudaStream_t values. */
+int b2_collective(b2_comm* comm, int collective, const void* const* send, void* const* recv,
+                  void* const* streams, size_t count, int dtype, int redop, int allow_in_place);
+/* What the last call resolved to: algo, grid, block, staged_in, staged_out, vectorized. */
+int b2_comm_last_call(const b2_comm* comm, int out[6]);
+
+/* Symmetric heap: `ptrs` receives one pointer per local rank. Collective over all processes. */
+int b2_comm_alloc_symmetric(b2_comm* comm, size_t bytes, void** ptrs);
+int b2_comm_free_symmetric(b2_comm* comm, void* const* ptrs);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,162 @@
+#include "b200ccl/c_api.h"
+
+#include "b200ccl/bootstrap.h"
+#include "b200ccl/communicator.h"
+
+#include <cstring>
+#include <exception>
+#include <stdexcept>
+#include <string>
+
+using namespace b200ccl;
+
+struct b2_comm {
+    std::unique_ptr<Communicator> comm;
+};
+struct b2_bootstrap {
+    std::unique_ptr<Bootstrap> bs;
+};
+
+namespace {
+thread_local std::string g_error;
+
+template <typename F>
+int guarded(F&& f) {
+    try {
+        f();
+        return 0;
+    } catch (const std::invalid_argument& e) {
+        g_error = e.what();
+        return 2;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return 1;
+    } catch (...) {
+        g_error = "unknown failure";
+        return 1;
+    }
+}
+
+CommunicatorConfig to_config(const int* devices, int ndev, const b2_config* c) {
+    CommunicatorConfig cfg;
+    cfg.devices.assign(devices, devices + ndev);
+    if (c) {
+        cfg.transport = static_cast<TransportKind>(c->transport);
+        cfg.algo = static_cast<Algo>(c->algo);
+        cfg.channels = c->channels;
+        cfg.staging_bytes = c->staging_bytes;
+        cfg.wait_timeout_ms = c->wait_timeout_ms;
+        cfg.loopback = c->loopback != 0;
+        cfg.loopback_ranks = c->loopback_ranks;
+        cfg.enable_nvls = c->enable_nvls != 0;
+    }
+    return cfg;
+}
+}  // namespace
+
+extern "C" {
+
+const char* b2_last_error(void) { return g_error.c_str(); }
+const char* b2_version(void) { return "0.1.0"; }
+
+int b2_parse_dtype(const char* t, int* out) { DType v; if (!parse_dtype(t, &v)) return 2; *out = static_cast<int>(v); return 0; }
+int b2_parse_redop(const char* t, int* out) { RedOp v; if (!parse_redop(t, &v)) return 2; *out = static_cast<int>(v); return 0; }
+int b2_parse_transport(const char* t, int* out) { TransportKind v; if (!parse_transport(t, &v)) return 2; *out = static_cast<int>(v); return 0; }
+int b2_parse_algo(const char* t, int* out) { Algo v; if (!parse_algo(t, &v)) return 2; *out = static_cast<int>(v); return 0; }
+const char* b2_dtype_name(int v) { return dtype_name(static_cast<DType>(v)); }
+const char* b2_redop_name(int v) { return redop_name(static_cast<RedOp>(v)); }
+const char* b2_transport_name(int v) { return transport_name(static_cast<TransportKind>(v)); }
+const char* b2_algo_name(int v) { return algo_name(static_cast<Algo>(v)); }
+double b2_busbw_gbs(int collective, double algbw, int nranks) {
+    return busbw_gbs(static_cast<Collective>(collective), algbw, nranks);
+}
+
+void b2_config_default(b2_config* cfg) {
+    std::memset(cfg, 0, sizeof(*cfg));
+    cfg->transport = static_cast<int>(TransportKind::Auto);
+    cfg->algo = static_cast<int>(Algo::Auto);
+    cfg->enable_nvls = 1;
+}
+
+int b2_bootstrap_create(const char* addr, int port, int rank, int size, int timeout_ms, b2_bootstrap** out) {
+    return guarded([&] {
+        auto bs = create_tcp_bootstrap(addr ? addr : "127.0.0.1", port, rank, size, timeout_ms > 0 ? timeout_ms : 60000);
+        *out = new b2_bootstrap{std::move(bs)};
+    });
+}
+void b2_bootstrap_destroy(b2_bootstrap* bs) { delete bs; }
+int b2_bootstrap_barrier(b2_bootstrap* bs) { return guarded([&] { bs->bs->barrier(); }); }
+int b2_bootstrap_allgather(b2_bootstrap* bs, const void* in, void* out, size_t bytes) {
+    return guarded([&] { bs->bs->allgather(in, out, bytes); });
+}
+
+int b2_comm_create(const int* devices, int ndev, const b2_config* cfg, b2_comm** out) {
+    return guarded([&] { *out = new b2_comm{create_communicator(to_config(devices, ndev, cfg))}; });
+}
+int b2_comm_create_bootstrap(b2_bootstrap* bs, const int* devices, int ndev, const b2_config* cfg, b2_comm** out) {
+    return guarded([&] { *out = new b2_comm{create_communicator_from_bootstrap(*bs->bs, to_config(devices, ndev, cfg))}; });
+}
+void b2_comm_destroy(b2_comm* comm) { delete comm; }
+
+int b2_comm_local_ranks(const b2_comm* c) { return c->comm->local_rank_count(); }
+int b2_comm_global_ranks(const b2_comm* c) { return c->comm->global_rank_count(); }
+int b2_comm_first_rank(const b2_comm* c) { return c->comm->first_global_rank(); }
+int b2_comm_transport(const b2_comm* c) { return static_cast<int>(c->comm->transport()); }
+int b2_comm_nvls(const b2_comm* c) { return c->comm->nvls_available() ? 1 : 0; }
+size_t b2_comm_describe(const b2_comm* c, char* buf, size_t cap) {
+    const std::string s = c->comm->describe();
+    if (buf && cap) {
+        const size_t n = s.size() < cap - 1 ? s.size() : cap - 1;
+        std::memcpy(buf, s.data(), n);
+        buf[n] = '\0';
+    }
+    return s.size();
+}
+int b2_comm_check_async_error(const b2_comm* c) { return guarded([&] { c->comm->check_async_error(); }); }
+
+int b2_collective(b2_comm* c, int collective, const void* const* send, void* const* recv, void* const* streams,
+                  size_t count, int dtype, int redop, int allow_in_place) {
+    return guarded([&] {
+        const int n = c->comm->local_rank_count();
+        CollectiveArgs a;
+        a.send_buffers.assign(send, send + n);
+        a.recv_buffers.assign(recv, recv + n);
+        for (int i = 0; i < n; ++i) a.streams.push_back(static_cast<cudaStream_t>(streams[i]));
+        a.count = count;
+        a.dtype = static_cast<DType>(dtype);
+        a.redop = static_cast<RedOp>(redop);
+        a.allow_in_place = allow_in_place != 0;
+        switch (collective) {
+            case 0: c->comm->all_reduce(a); break;
+            case 1: c->comm->reduce_scatter(a); break;
+            case 2: c->comm->all_gather(a); break;
+            default: throw std::invalid_argument("unknown collective id");
+        }
+    });
+}
+
+int b2_comm_last_call(const b2_comm* c, int out[6]) {
+    const CallInfo i = c->comm->last_call();
+    out[0] = static_cast<int>(i.algo);
+    out[1] = i.grid;
+    out[2] = i.block;
+    out[3] = i.staged_in;
+    out[4] = i.staged_out;
+    out[5] = i.vectorized;
+    return 0;
+}
+
+int b2_comm_alloc_symmetric(b2_comm* c, size_t bytes, void** ptrs) {
+    return guarded([&] {
+        auto v = c->comm->alloc_symmetric(bytes);
+        for (size_t i = 0; i < v.size(); ++i) ptrs[i] = v[i];
+    });
+}
+int b2_comm_free_symmetric(b2_comm* c, void* const* ptrs) {
+    return guarded([&] {
+        std::vector<void*> v(ptrs, ptrs + c->comm->local_rank_count());
+        c->comm->free_symmetric(v);
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,138 @@
+#include "sched/plan.h"
+
+#include "core/env.h"
+
+#include <algorithm>
+
+namespace b200ccl::sched {
+
+Tuning default_tuning() {
+    Tuning t{};
+    // One-shot moves (n-1)·S per rank against two-shot's 2(n-1)/n·S but has no second hop.
+    for (int n = 0; n <= kMaxRanks; ++n) t.oneshot_max_bytes[n] = 256u << 10;
+    t.oneshot_max_bytes[2] = 1u << 20;   // at two ranks both move S; one-shot only stores locally
+    t.oneshot_max_bytes[4] = 256u << 10;
+    t.oneshot_max_bytes[8] = 128u << 10;
+    t.nvls_min_bytes = 64u << 10;
+    t.max_ctas = 64;
+    t.bytes_per_cta = 32u << 10;
+    return t;
+}
+
+Tuning tuning_from_env() {
+    Tuning t = default_tuning();
+    if (env::get("B200CCL_ONESHOT_MAX_BYTES")) {
+        const std::size_t v = env::get_bytes("B200CCL_ONESHOT_MAX_BYTES", 0);
+        for (int n = 0; n <= kMaxRanks; ++n) t.oneshot_max_bytes[n] = v;
+    }
+    t.nvls_min_bytes = env::get_bytes("B200CCL_NVLS_MIN_BYTES", t.nvls_min_bytes);
+    t.max_ctas = static_cast<int>(env::get_int("B200CCL_MAX_CTAS", t.max_ctas));
+    t.bytes_per_cta = env::get_bytes("B200CCL_BYTES_PER_CTA", t.bytes_per_cta);
+    return t;
+}
+
+std::size_t message_bytes(const CallShape& s) {
+    const std::size_t one = s.count * dtype_size(s.dtype);
+    return s.collective == Collective::AllReduce ? one : one * static_cast<std::size_t>(s.nranks);
+}
+
+namespace {
+
+int grid_for(std::size_t bytes_this_rank_handles, const Tuning& t, int cap) {
+    const std::size_t per = std::max<std::size_t>(t.bytes_per_cta, 1);
+    std::size_t g = (bytes_this_rank_handles + per - 1) / per;
+    g = std::max<std::size_t>(g, 1);
+    return static_cast<int>(std::min<std::size_t>(g, static_cast<std::size_t>(std::max(cap, 1))));
+}
+
+bool nvls_usable(const CallShape& s) {
+    if (!s.wide || s.nranks < 2) return false;
+    switch (s.collective) {
+        case Collective::AllReduce:
+            return (s.redop == RedOp::Sum || s.redop == RedOp::Avg) && s.input_multicast && s.output_multicast;
+        case Collective::ReduceScatter:
+            return (s.redop == RedOp::Sum || s.redop == RedOp::Avg) && s.input_multicast;
+        case Collective::AllGather:
+            return s.output_multicast;
+    }
+    return false;
+}
+
+}  // namespace
+
+Plan make_plan(const CallShape& s, Algo forced, const Tuning& t) {
+    Plan p;
+    const int cap = std::min(s.max_ctas > 0 ? s.max_ctas : t.max_ctas, t.max_ctas);
+    const std::size_t bytes = message_bytes(s);
+    const std::size_t esz = dtype_size(s.dtype);
+
+    if (s.ring_only || forced == Algo::Ring) {
+        p.algo = Algo::Ring;
+        p.grid = 0;  // the ring path sizes itself by channels
+        return p;
+    }
+    if (s.nranks == 1) {
+        p.algo = Algo::OneShot;  // degenerates to a local copy (with the avg scale of 1)
+        p.grid = grid_for(bytes, t, cap);
+        p.gather_mode = 1;
+        return p;
+    }
+
+    const bool nvls_ok = nvls_usable(s);
+    if (forced == Algo::Nvls && !nvls_ok) {
+        p.error = "algo nvls needs symmetric (multicast-bound) buffers, 16-byte alignment and sum/avg";
+        return p;
+    }
+
+    if (s.collective == Collective::AllGather) {
+        if (forced == Algo::Nvls || (forced == Algo::Auto && nvls_ok && bytes >= t.nvls_min_bytes)) {
+            p.algo = Algo::Nvls;
+            p.gather_mode = 2;
+        } else if (s.peers_write_output) {
+            p.algo = Algo::OneShot;
+            p.gather_mode = 0;
+        } else {
+            p.algo = Algo::OneShot;
+            p.gather_mode = 1;
+            p.stage_in = !s.peers_read_input;
+        }
+        p.grid = grid_for(s.count * esz * (p.gather_mode == 1 ? s.nranks : 1), t, cap);
+        return p;
+    }
+
+    if (s.collective == Collective::ReduceScatter) {
+        p.algo = (forced == Algo::Nvls || (forced == Algo::Auto && nvls_ok && bytes >= t.nvls_min_bytes))
+                     ? Algo::Nvls : Algo::OneShot;
+        p.stage_in = p.algo != Algo::Nvls && !s.peers_read_input;
+        p.grid = grid_for(s.count * esz * (p.stage_in ? s.nranks : 1), t, cap);
+        return p;
+    }
+
+    // AllReduce
+    Algo algo = forced;
+    if (algo == Algo::Auto) {
+        if (nvls_ok && bytes >= t.nvls_min_bytes) algo = Algo::Nvls;
+        else if (bytes <= t.oneshot_max_bytes[std::min(s.nranks, kMaxRanks)] && !s.in_place) algo = Algo::OneShot;
+        else algo = Algo::TwoShot;
+    }
+    if (algo == Algo::OneShot && s.in_place && s.peers_read_input) {
+        p.error = "one-shot all_reduce cannot run in place on buffers that peers read directly";
+        return p;
+    }
+    p.algo = algo;
+    if (algo == Algo::Nvls) {
+        p.grid = grid_for(bytes / s.nranks, t, cap);
+    } else if (algo == Algo::OneShot) {
+        p.stage_in = !s.peers_read_input;
+        p.grid = grid_for(bytes, t, cap);
+    } else {
+        p.stage_in = !s.peers_read_input;
+        p.stage_out = !s.peers_write_output;
+        // Staging works on (input arena, output arena) pairs: if either side is staged the
+        // kernel still reads/writes the other side in place.
+        p.grid = grid_for(bytes / s.nranks * (p.stage_in || p.stage_out ? s.nranks : 1), t, cap);
+    }
+    return p;
+}
+
+}  // namespace b200ccl::sched

@@ -1,0 +1,58 @@
+// Per-call planning: which algorithm, how many CTAs, and whether a buffer must pass through
+// the staging arena. Pure functions of the call shape, so that every rank (and every process)
+// reaches the same decision without talking, and so that the logic is testable without a GPU.
+//
+// nano-nccl has a single algorithm and a fixed 4-CTA launch, so it has no counterpart; its
+// nearest relative is the per-edge transport plan (src/transport/p2p/p2p_topology.h:13-36).
+#pragma once
+
+#include "b200ccl/types.h"
+
+#include <cstddef>
+#include <string>
+
+namespace b200ccl::sched {
+
+struct CallShape {
+    Collective collective = Collective::AllReduce;
+    DType dtype = DType::Float;
+    RedOp redop = RedOp::Sum;
+    int nranks = 1;
+    std::size_t count = 0;       // the API's `count`
+    bool wide = false;           // every pointer 16-byte aligned and every block a multiple of 16 bytes
+    bool peers_read_input = false;    // peers can load this call's input directly
+    bool peers_write_output = false;  // peers can store into this call's output directly
+    bool input_multicast = false;     // input has a multicast alias (NVLS ld_reduce possible)
+    bool output_multicast = false;    // output has a multicast alias (NVLS broadcast possible)
+    bool in_place = false;
+    bool ring_only = false;      // transport without all-pairs peer access: ring is the only choice
+    int max_ctas = 64;
+};
+
+struct Plan {
+    Algo algo = Algo::TwoShot;
+    int grid = 1;
+    bool stage_in = false;
+    bool stage_out = false;
+    int gather_mode = 0;  // AllGather: 0 push, 1 pull, 2 nvls
+    std::string error;    // non-empty → the request cannot be satisfied (forced algo impossible)
+};
+
+// Crossover points. Defaults come from measurements on 8×B200; each can be overridden by
+// environment (B200CCL_ONESHOT_MAX_BYTES, B200CCL_NVLS_MIN_BYTES, B200CCL_MAX_CTAS).
+struct Tuning {
+    std::size_t oneshot_max_bytes[kMaxRanks + 1];  // per nranks: AllReduce sizes up to this use one-shot
+    std::size_t nvls_min_bytes = 0;                // NVLS from this size up (when available)
+    int max_ctas = 64;
+    std::size_t bytes_per_cta = 0;                 // work given to one CTA before another is added
+};
+Tuning default_tuning();
+Tuning tuning_from_env();
+
+Plan make_plan(const CallShape& shape, Algo forced, const Tuning& tuning);
+
+// Bytes moved through the API per rank: count*size for AllReduce, the full count*nranks*size
+// buffer for ReduceScatter (input) and AllGather (output).
+std::size_t message_bytes(const CallShape& shape);
+
+}  // namespace b200ccl::sched
