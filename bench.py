@@ -1,0 +1,450 @@
+#!/usr/bin/env python
+"""Headline benchmark: AllReduce bus bandwidth (GB/s) on N B200s of one node.
+
+One step = one out-of-place float32 sum AllReduce of 64 MiB per rank (the largest size of the
+reference's published table, performance.md:28-32) through this package's public API, one process
+per GPU. Prints ONE JSON line from rank 0.
+
+    python bench.py --gpus 1 --steps 200 --warmup 20
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 200 --warmup 20
+    ... bench.py --impl reference   # the unmodified reference's own benchmark binary
+    ... bench.py --impl nccl        # torch.distributed NCCL on the same buffers (comparator)
+    ... bench.py --impl nccl-ring   # NCCL pinned to Ring + Simple, 4 channels, 32 MiB buffer
+
+Timing: W warm-up steps, then exactly K steps between a barrier + device synchronize on both
+sides, measured with CUDA events on the launching stream, maximum over ranks. Successive steps
+rotate over buffer sets whose total exceeds the 126 MB L2. SM clocks and throttle reasons are
+sampled with nvidia-smi during the timed region.
+"""
+import argparse
+import json
+import os
+import re
+import socket
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HEADLINE_BYTES = 64 << 20
+BASELINE_BUSBW = 23.12  # nano-nccl, 4x A6000, float sum, 64 MiB (performance.md:32)
+L2_BYTES = 126 * 1000 * 1000
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl", "nccl-ring"])
+    ap.add_argument("--bytes", type=int, default=HEADLINE_BYTES)
+    ap.add_argument("--dtype", default="float", choices=["float", "fp16", "bf16"])
+    ap.add_argument("--op", default="sum", choices=["sum", "avg", "max", "min"])
+    ap.add_argument("--buffers", default="symmetric", choices=["symmetric", "plain"],
+                    help="symmetric: tensors from Communicator.empty (peer-mapped, NVLS-capable); plain: torch.empty")
+    ap.add_argument("--algo", default="auto")
+    ap.add_argument("--sweep", action="store_true", help="also measure 1 KiB..1 GiB and add it under 'sweep'")
+    ap.add_argument("--sweep-max", type=int, default=1 << 30)
+    ap.add_argument("--ref-transport", default="p2p", choices=["auto", "p2p", "shm"])
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks
+
+class ClockSampler:
+    """Runs `nvidia-smi -lms 200` while the timed region executes and summarises one GPU's samples."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        clocks, maxes, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9 or parts[0] != str(self.gpu_index):
+                    continue
+                try:
+                    clocks.append(float(parts[1]))
+                    maxes.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        clocks.sort()
+        med = clocks[len(clocks) // 2] if clocks else None
+        return {"sm_mhz": med, "sm_max_mhz": max(maxes) if maxes else None, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+# ---------------------------------------------------------------------------------------------
+# helpers
+
+def free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    return rank, world, local
+
+
+def init_dist(backend):
+    import torch.distributed as dist
+    rank, world, _ = dist_env()
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group(backend=backend, rank=rank, world_size=world)
+    return dist
+
+
+def busbw(nbytes, seconds, n):
+    alg = nbytes / seconds / 1e9
+    return alg * 2 * (n - 1) / n if n > 1 else alg
+
+
+TORCH_DTYPES = {}
+
+
+def torch_dtype(name):
+    import torch
+    return {"float": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[name]
+
+
+# ---------------------------------------------------------------------------------------------
+# our arm and the NCCL comparator share the timing harness
+
+class Runner:
+    def __init__(self, args):
+        import torch
+        self.torch = torch
+        self.args = args
+        self.rank, self.world, self.local = dist_env()
+        if self.world != args.gpus:
+            if self.world == 1 and args.gpus > 1:
+                raise SystemExit("--gpus N > 1 needs one process per GPU: launch with torch.distributed.run")
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        self.is_nccl = args.impl.startswith("nccl")
+        if args.impl == "nccl-ring":
+            os.environ.update({"NCCL_ALGO": "Ring", "NCCL_PROTO": "Simple", "NCCL_MIN_NCHANNELS": "4",
+                               "NCCL_MAX_NCHANNELS": "4", "NCCL_BUFFSIZE": "33554432"})
+        self.dist = init_dist("nccl")
+        self.comm = None
+        if not self.is_nccl:
+            import nano_nccl_b200 as nn
+            port = [free_port() if self.rank == 0 else 0]
+            if self.world > 1:
+                self.dist.broadcast_object_list(port, src=0)
+            self.comm = nn.Communicator(devices=[self.local], rank=self.rank, world_size=self.world,
+                                        addr=os.environ.get("MASTER_ADDR", "127.0.0.1"), port=port[0], algo=args.algo)
+        self.launches = 0
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, value):
+        if self.world == 1:
+            return value
+        t = self.torch.tensor([value], dtype=self.torch.float64, device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def alloc(self, numel, dtype):
+        if self.comm is not None and self.args.buffers == "symmetric":
+            return self.comm.empty(numel, dtype)
+        return self.torch.empty(numel, dtype=dtype, device=self.dev)
+
+    def all_reduce(self, out, inp, op):
+        if self.is_nccl:
+            # NCCL through torch is in-place; reduce `inp` into itself (same traffic as out-of-place).
+            ops = {"sum": self.dist.ReduceOp.SUM, "avg": self.dist.ReduceOp.AVG, "max": self.dist.ReduceOp.MAX,
+                   "min": self.dist.ReduceOp.MIN}
+            if self.world > 1:
+                self.dist.all_reduce(inp, op=ops[op])
+        else:
+            self.comm.all_reduce(out, inp, op=op)
+        self.launches += 1
+
+    def make_sets(self, nbytes, dtype):
+        esize = self.torch.empty((), dtype=dtype).element_size()
+        numel = max(nbytes // esize, 1)
+        per_set = 2 * numel * esize
+        nsets = int(min(8, max(1, -(-4 * L2_BYTES // per_set))))
+        sets = []
+        for s in range(nsets):
+            inp = self.alloc(numel, dtype)
+            out = self.alloc(numel, dtype)
+            gen = self.torch.Generator(device=self.dev).manual_seed(1000 * self.rank + s)
+            inp.copy_((self.torch.rand(numel, device=self.dev, generator=gen) * 2 - 1).to(dtype))
+            sets.append((inp, out))
+        return sets, numel, nsets * per_set
+
+    def time_steps(self, sets, op, warmup, steps):
+        torch = self.torch
+        for i in range(warmup):
+            inp, out = sets[i % len(sets)]
+            self.all_reduce(out, inp, op)
+        self.barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.launches = 0
+        start.record()
+        for i in range(steps):
+            inp, out = sets[i % len(sets)]
+            self.all_reduce(out, inp, op)
+        stop.record()
+        self.barrier()
+        if self.comm is not None:
+            self.comm.check_async_error()
+        return self.max_over_ranks(start.elapsed_time(stop) / 1e3)
+
+    def verify(self, sets, numel, dtype, op):
+        """Recomputes the expected result of set 0 from every rank's seeded input (fp32) and counts mismatches."""
+        torch = self.torch
+        if self.is_nccl:
+            return None
+        inp, out = sets[0]
+        self.all_reduce(out, inp, op)
+        torch.cuda.synchronize()
+        acc = None
+        for r in range(self.world):
+            gen = torch.Generator(device=self.dev).manual_seed(1000 * r)
+            x = (torch.rand(numel, device=self.dev, generator=gen) * 2 - 1).to(dtype).float()
+            if acc is None:
+                acc = x
+            elif op in ("sum", "avg"):
+                acc += x
+            elif op == "max":
+                acc = torch.maximum(acc, x)
+            else:
+                acc = torch.minimum(acc, x)
+        if op == "avg":
+            acc /= self.world
+        eps = {"float": 1e-5, "fp16": 1e-2, "bf16": 1e-1}[self.args.dtype]
+        wrong = int(((out.float() - acc).abs() > eps).sum().item())
+        return int(self.max_over_ranks(float(wrong)))
+
+    def time_e2e(self, sets, numel, dtype, op, warmup, steps):
+        """Same metric end to end: every step copies its input from pinned host memory, runs the
+        collective through the public API and reads a slice of the result back to the host."""
+        torch = self.torch
+        host_in = [torch.empty(numel, dtype=dtype).pin_memory() for _ in sets]
+        for h, (inp, _) in zip(host_in, sets):
+            h.copy_(inp)
+        res_elems = min(numel, 1024)
+        host_out = torch.empty(res_elems, dtype=dtype).pin_memory()
+        h2d = numel * host_in[0].element_size()
+        d2h = res_elems * host_out.element_size()
+
+        def step(i):
+            inp, out = sets[i % len(sets)]
+            inp.copy_(host_in[i % len(sets)], non_blocking=True)
+            self.all_reduce(out, inp, op)
+            src = inp if self.is_nccl else out
+            host_out.copy_(src[:res_elems], non_blocking=True)
+
+        for i in range(warmup):
+            step(i)
+        self.barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            step(i)
+        stop.record()
+        self.barrier()
+        return self.max_over_ranks(start.elapsed_time(stop) / 1e3), h2d, d2h
+
+
+def run_measured(args):
+    import torch
+    r = Runner(args)
+    dtype = torch_dtype(args.dtype)
+    sets, numel, working = r.make_sets(args.bytes, dtype)
+    nbytes = numel * sets[0][0].element_size()
+    wrong = r.verify(sets, numel, dtype, args.op)
+    sampler = ClockSampler(r.local)
+    if r.rank == 0:
+        sampler.start()
+    seconds = r.time_steps(sets, args.op, max(args.warmup, 3), args.steps)
+    launches = r.launches
+    clocks = sampler.stop() if r.rank == 0 else None
+    e2e_seconds, h2d, d2h = r.time_e2e(sets, numel, dtype, args.op, max(args.warmup // 2, 3), max(args.steps // 4, 5))
+    e2e_steps = max(args.steps // 4, 5)
+    info = r.comm.last_call() if r.comm is not None else {"algo": args.impl}
+
+    sweep = None
+    if args.sweep:
+        sweep = []
+        size = 1024
+        while size <= args.sweep_max:
+            s_sets, s_numel, _ = r.make_sets(size, dtype)
+            iters = 200 if size <= (1 << 20) else (50 if size <= (64 << 20) else 10)
+            t = r.time_steps(s_sets, args.op, 5, iters)
+            b = s_numel * s_sets[0][0].element_size()
+            sweep.append({"bytes": b, "time_us": round(t / iters * 1e6, 2), "busbw_gbs": round(busbw(b, t / iters, r.world), 2),
+                          "algo": (r.comm.last_call()["algo"] if r.comm is not None else args.impl)})
+            del s_sets
+            torch.cuda.empty_cache()
+            size *= 2
+
+    if r.rank == 0:
+        per_step = seconds / args.steps
+        value = busbw(nbytes, per_step, r.world)
+        e2e_value = busbw(nbytes, e2e_seconds / e2e_steps, r.world)
+        line = {
+            "metric": "allreduce_busbw_gbs_64MiB_float_sum" if r.world > 1 else "allreduce_algbw_gbs_64MiB_float_sum_single_gpu",
+            "value": round(value, 2),
+            "unit": "GB/s",
+            "impl": args.impl,
+            "n_gpus": r.world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": round(per_step * 1e3, 5),
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": round(value / BASELINE_BUSBW, 2),
+            "dtype": args.dtype,
+            "data": "synthetic: uniform[-1,1) seeded per rank, device-generated",
+            "wrong": wrong,
+            "aggregate_gbs": round(value * r.world, 2),
+            "config": {
+                "model": "AllReduce (collective library; no neural model)",
+                "collective": "all_reduce", "redop": args.op, "bytes_per_rank": nbytes, "global_batch": nbytes * r.world,
+                "seq_len": numel, "parallelism": f"allreduce{r.world}",
+                "buffers": args.buffers if r.comm is not None else "torch.empty (NCCL in place)",
+                "algo": info.get("algo"), "grid": info.get("grid"),
+                "l2": f"rotating over {len(sets)} buffer sets, {working >> 20} MiB working set > 126 MB L2",
+                "busbw_formula": "bytes/time * 2(n-1)/n; at n=1 the factor is 0, so the single-GPU value is bytes/time of the local copy kernel",
+                "timing": "CUDA events around K back-to-back steps, max over ranks",
+            },
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": round(e2e_seconds / e2e_steps * 1e3, 5),
+                    "note": "each step: pinned-host -> device copy of the whole input, all_reduce via Communicator.all_reduce, device -> pinned-host read of the first 1024 result elements"},
+            "gpu_launches": launches if r.comm is not None else 0,
+        }
+        if sweep is not None:
+            line["sweep"] = sweep
+        print(json.dumps(line), flush=True)
+    if r.comm is not None:
+        del sets
+        r.comm.close()
+    if r.world > 1:
+        r.dist.barrier()
+        r.dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------
+# reference arm: the unmodified nano-nccl benchmark binary, built by baseline/build_reference.sh
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    n = args.gpus
+    result = None
+    if rank == 0:
+        binary = os.path.join(ROOT, "baseline", "_ref", "bin", f"nano_nccl_all_reduce_bench_n{n}")
+        if n < 2:
+            result = {"impl": "reference", "unavailable": "the reference fixes its rank count at build time and is not built or documented for 1 rank"}
+        elif not os.path.exists(binary):
+            result = {"impl": "reference", "unavailable": f"{os.path.relpath(binary, ROOT)} missing: run baseline/build_reference.sh"}
+        else:
+            result = reference_measure(binary, args, n)
+    if world > 1:
+        dist = init_dist("gloo")
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+
+
+def reference_measure(binary, args, n):
+    cmd = [binary, "--dtype", args.dtype, "--redop", args.op, "--transport", args.ref_transport,
+           "-b", str(args.bytes), "-e", str(args.bytes), "-f", "2", "-w", str(max(args.warmup, 3)), "-n", str(args.steps)]
+    sampler = ClockSampler(0)
+    sampler.start()
+    t0 = time.time()
+    try:
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    except subprocess.TimeoutExpired:
+        sampler.stop()
+        return {"impl": "reference", "unavailable": "reference benchmark did not finish within 600 s"}
+    wall = time.time() - t0
+    clocks = sampler.stop()
+    row = None
+    for line in proc.stdout.splitlines():
+        if line.startswith("#") or not line.strip():
+            continue
+        parts = line.split()
+        if len(parts) >= 11 and parts[4].isdigit():
+            row = parts
+    if row is None:
+        tail = (proc.stderr or proc.stdout).strip().splitlines()[-1:] or ["no output"]
+        return {"impl": "reference", "unavailable": f"reference benchmark gave no result row (exit {proc.returncode}): {tail[0][:200]}"}
+    time_us, algbw, bus, wrong = float(row[6]), float(row[7]), float(row[8]), int(row[9])
+    return {
+        "metric": "allreduce_busbw_gbs_64MiB_float_sum", "value": bus, "unit": "GB/s", "impl": "reference",
+        "n_gpus": n, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(time_us / 1e3, 5),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": round(bus / BASELINE_BUSBW, 2), "dtype": args.dtype,
+        "data": "synthetic: the reference benchmark's own arithmetic input pattern", "wrong": wrong,
+        "config": {"model": "AllReduce (collective library; no neural model)", "collective": "all_reduce", "redop": args.op,
+                   "bytes_per_rank": int(row[4]), "global_batch": int(row[4]) * n, "seq_len": int(row[5]),
+                   "parallelism": f"allreduce{n}", "transport": row[3], "requested_transport": args.ref_transport,
+                   "binary": f"nano_nccl_all_reduce_bench built with -DNANO_NCCL_NRANKS={n} -DNANO_NCCL_CUDA_ARCH=100",
+                   "timing": "the reference's own host steady_clock around the batch (its stock method)",
+                   "l2": "single buffer pair (the reference's stock benchmark)"},
+        "clocks": clocks, "wall_seconds": round(wall, 2),
+        "e2e": None, "gpu_launches": args.steps * n,
+    }
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_measured(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,208 @@
+"""Python face of the communicator: create one per process (one GPU each) or one for several
+GPUs of this process, and run all_reduce / reduce_scatter / all_gather on torch tensors.
+
+The reference library (nano-nccl) has no Python layer; its C++ calls
+(include/nano_nccl/communicator.h:31-58) are what these methods forward to.
+"""
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+_OPS = {"sum": 0, "avg": 1, "max": 2, "min": 3}
+_COLL = {"all_reduce": 0, "reduce_scatter": 1, "all_gather": 2}
+_ALGO_NAMES = ["auto", "oneshot", "twoshot", "nvls", "ring"]
+
+
+class _SymmetricBlock:
+    """Owner of one symmetric allocation; exposes it to torch through the CUDA array interface."""
+
+    def __init__(self, comm, ptr, nbytes):
+        self.comm, self.ptr, self.nbytes = comm, ptr, nbytes
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None}
+
+
+class Communicator:
+    """One communicator.
+
+    * ``Communicator(devices=[0, 1, ...])`` — this process drives all listed GPUs (tensors are then
+      passed as lists, one per GPU).
+    * ``Communicator.from_env()`` / ``Communicator(rank=, world_size=, addr=, port=)`` — one process
+      per GPU; peer memory is shared through exported allocations.
+    * ``Communicator(devices=[0], loopback_ranks=N)`` — N ranks emulated on one GPU (tests, profiling).
+    """
+
+    def __init__(self, devices=None, rank=None, world_size=None, addr="127.0.0.1", port=None,
+                 transport="auto", algo="auto", loopback_ranks=0, wait_timeout_ms=0.0,
+                 staging_bytes=0, enable_nvls=True, channels=0):
+        lib = _lib.load()
+        self._lib = lib
+        self._handle = ctypes.c_void_p()
+        self._bootstrap = ctypes.c_void_p()
+        self._blocks = []
+        cfg = _lib.B2Config()
+        lib.b2_config_default(ctypes.byref(cfg))
+        t, a = ctypes.c_int(), ctypes.c_int()
+        if lib.b2_parse_transport(transport.encode(), ctypes.byref(t)) != 0 and transport != "socket":
+            raise ValueError(f"unknown transport '{transport}'")
+        cfg.transport = 3 if transport == "socket" else t.value
+        if lib.b2_parse_algo(algo.encode(), ctypes.byref(a)) != 0:
+            raise ValueError(f"unknown algo '{algo}'")
+        cfg.algo = a.value
+        cfg.loopback = 1 if loopback_ranks else 0
+        cfg.loopback_ranks = int(loopback_ranks)
+        cfg.wait_timeout_ms = float(wait_timeout_ms)
+        cfg.staging_bytes = int(staging_bytes)
+        cfg.enable_nvls = 1 if enable_nvls else 0
+        cfg.channels = int(channels)
+        if devices is None:
+            devices = [torch.cuda.current_device()]
+        self.devices = list(devices)
+        dev_arr = (ctypes.c_int * len(self.devices))(*self.devices)
+        if world_size is not None and world_size > 1:
+            if port is None:
+                raise ValueError("multi-process communicator needs a port")
+            _lib.check(lib.b2_bootstrap_create(addr.encode(), int(port), int(rank), int(world_size), 120000,
+                                               ctypes.byref(self._bootstrap)))
+            _lib.check(lib.b2_comm_create_bootstrap(self._bootstrap, dev_arr, len(self.devices), ctypes.byref(cfg),
+                                                    ctypes.byref(self._handle)))
+        else:
+            _lib.check(lib.b2_comm_create(dev_arr, len(self.devices), ctypes.byref(cfg), ctypes.byref(self._handle)))
+        self.local_ranks = lib.b2_comm_local_ranks(self._handle)
+        self.world_size = lib.b2_comm_global_ranks(self._handle)
+        self.rank = lib.b2_comm_first_rank(self._handle)
+
+    @classmethod
+    def from_env(cls, port=None, **kw):
+        """One process per GPU, laid out by RANK / WORLD_SIZE / LOCAL_RANK / MASTER_ADDR (torchrun).
+
+        The rendezvous port defaults to B200CCL_PORT, else MASTER_PORT + 1000 + 7."""
+        rank = int(os.environ.get("RANK", "0"))
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        local = int(os.environ.get("LOCAL_RANK", str(rank)))
+        addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
+        if port is None:
+            port = int(os.environ.get("B200CCL_PORT", int(os.environ.get("MASTER_PORT", "29500")) + 1007))
+        torch.cuda.set_device(local)
+        return cls(devices=[local], rank=rank, world_size=world, addr=addr, port=port, **kw)
+
+    # -- properties -------------------------------------------------------------------------
+    @property
+    def transport(self):
+        return self._lib.b2_transport_name(self._lib.b2_comm_transport(self._handle)).decode()
+
+    @property
+    def nvls(self):
+        return bool(self._lib.b2_comm_nvls(self._handle))
+
+    def describe(self):
+        n = self._lib.b2_comm_describe(self._handle, None, 0)
+        buf = ctypes.create_string_buffer(n + 1)
+        self._lib.b2_comm_describe(self._handle, buf, n + 1)
+        return buf.value.decode()
+
+    def last_call(self):
+        out = (ctypes.c_int * 6)()
+        self._lib.b2_comm_last_call(self._handle, out)
+        return {"algo": _ALGO_NAMES[out[0]], "grid": out[1], "block": out[2], "staged_in": bool(out[3]),
+                "staged_out": bool(out[4]), "vectorized": bool(out[5])}
+
+    def check_async_error(self):
+        _lib.check(self._lib.b2_comm_check_async_error(self._handle))
+
+    # -- symmetric memory ----------------------------------------------------------------------
+    def empty(self, shape, dtype=torch.float32):
+        """Symmetric tensor(s): mapped on every peer (and multicast-bound when NVLS is available), so
+        collectives on them need no staging. COLLECTIVE: every process calls it with the same shape, in
+        the same order. Returns one tensor (one local rank) or a list (several local GPUs)."""
+        if isinstance(shape, int):
+            shape = (shape,)
+        numel = 1
+        for s in shape:
+            numel *= int(s)
+        esize = torch.empty((), dtype=dtype).element_size()
+        nbytes = max(numel * esize, 16)
+        ptrs = (ctypes.c_void_p * self.local_ranks)()
+        _lib.check(self._lib.b2_comm_alloc_symmetric(self._handle, nbytes, ptrs))
+        outs = []
+        for i in range(self.local_ranks):
+            dev = self.devices[0] if len(self.devices) == 1 else self.devices[i]
+            block = _SymmetricBlock(self, ptrs[i], nbytes)
+            self._blocks.append(block)
+            with torch.cuda.device(dev):
+                raw = torch.as_tensor(block, device=f"cuda:{dev}")
+            outs.append(raw[: numel * esize].view(dtype).view(*shape))
+        return outs[0] if self.local_ranks == 1 else outs
+
+    # -- collectives -----------------------------------------------------------------------------
+    def _run(self, coll, outs, inps, op, streams, count, in_place=False):
+        single = isinstance(inps, torch.Tensor)
+        if single:
+            inps, outs = [inps], [outs]
+        if len(inps) != self.local_ranks or len(outs) != self.local_ranks:
+            raise ValueError(f"need one tensor per local rank ({self.local_ranks})")
+        dtype = inps[0].dtype
+        if dtype not in _DTYPES:
+            raise ValueError(f"unsupported dtype {dtype}")
+        for t in list(inps) + list(outs):
+            if not t.is_cuda or not t.is_contiguous() or t.dtype != dtype:
+                raise ValueError("tensors must be contiguous CUDA tensors of one dtype")
+        if streams is None:
+            streams = []
+            for t in inps:
+                streams.append(torch.cuda.current_stream(t.device).cuda_stream)
+        elif not isinstance(streams, (list, tuple)):
+            streams = [streams]
+        streams = [s.cuda_stream if hasattr(s, "cuda_stream") else int(s) for s in streams]
+        n = self.local_ranks
+        send = (ctypes.c_void_p * n)(*[t.data_ptr() for t in inps])
+        recv = (ctypes.c_void_p * n)(*[t.data_ptr() for t in outs])
+        st = (ctypes.c_void_p * n)(*streams)
+        _lib.check(self._lib.b2_collective(self._handle, _COLL[coll], send, recv, st, count, _DTYPES[dtype], _OPS[op],
+                                           1 if in_place else 0))
+
+    def all_reduce(self, out, inp=None, op="sum", stream=None):
+        """out = reduce(inp over all ranks). ``inp=None`` (or the same tensor) reduces in place."""
+        if inp is None:
+            inp = out
+        first_in = inp if isinstance(inp, torch.Tensor) else inp[0]
+        first_out = out if isinstance(out, torch.Tensor) else out[0]
+        in_place = first_in.data_ptr() == first_out.data_ptr()
+        self._run("all_reduce", out, inp, op, stream, first_in.numel(), in_place)
+        return out
+
+    def reduce_scatter(self, out, inp, op="sum", stream=None):
+        """Rank r's ``out`` (numel = inp.numel() / world_size) receives block r of the reduction."""
+        first_out = out if isinstance(out, torch.Tensor) else out[0]
+        first_in = inp if isinstance(inp, torch.Tensor) else inp[0]
+        if first_in.numel() != first_out.numel() * self.world_size:
+            raise ValueError("reduce_scatter: input must hold world_size blocks of the output's size")
+        self._run("reduce_scatter", out, inp, op, stream, first_out.numel())
+        return out
+
+    def all_gather(self, out, inp, stream=None):
+        """``out`` (numel = inp.numel() * world_size) receives every rank's ``inp``, in rank order."""
+        first_out = out if isinstance(out, torch.Tensor) else out[0]
+        first_in = inp if isinstance(inp, torch.Tensor) else inp[0]
+        if first_out.numel() != first_in.numel() * self.world_size:
+            raise ValueError("all_gather: output must hold world_size blocks of the input's size")
+        self._run("all_gather", out, inp, "sum", stream, first_in.numel())
+        return out
+
+    def close(self):
+        if self._handle:
+            self._lib.b2_comm_destroy(self._handle)
+            self._handle = ctypes.c_void_p()
+        if self._bootstrap:
+            self._lib.b2_bootstrap_destroy(self._bootstrap)
+            self._bootstrap = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
