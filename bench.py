@@ -60,7 +60,7 @@ def parse_args():
 class ClockSampler:
     """Runs `nvidia-smi -lms 200` while the timed region executes and summarises one GPU's samples."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    QUERY = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
@@ -74,12 +74,14 @@ class ClockSampler:
             os.close(fd)
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=self.out, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def stop(self, window=None):
+        """Summarises the samples of this GPU; `window` = (t0, t1) wall-clock seconds keeps only samples
+        taken inside it (falls back to all samples when none fall inside)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -88,26 +90,31 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
         self.out.close()
-        clocks, maxes, reasons = [], [], set()
+        import datetime
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         with open(self.path) as f:
             for line in f:
                 parts = [p.strip() for p in line.split(",")]
-                if len(parts) < 9 or parts[0] != str(self.gpu_index):
+                if len(parts) < 10 or parts[1] != str(self.gpu_index):
                     continue
                 try:
-                    clocks.append(float(parts[1]))
-                    maxes.append(float(parts[2]))
+                    ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    rows.append((ts, float(parts[2]), float(parts[3]), float(parts[4]),
+                                 [n for n, v in zip(names, parts[6:10]) if v.lower().startswith("active")]))
                 except ValueError:
                     continue
-                for name, val in zip(names, parts[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
         os.unlink(self.path)
-        clocks.sort()
-        med = clocks[len(clocks) // 2] if clocks else None
-        return {"sm_mhz": med, "sm_max_mhz": max(maxes) if maxes else None, "reasons": sorted(reasons),
-                "samples": len(clocks)}
+        inside = [r for r in rows if window and window[0] <= r[0] <= window[1]]
+        scope = "timed region"
+        if not inside:
+            inside, scope = rows, "whole run (no sample fell inside the timed region)"
+        clocks = sorted(r[1] for r in inside)
+        reasons = sorted({n for r in inside for n in r[4]})
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None,
+                "sm_max_mhz": max((r[2] for r in inside), default=None),
+                "power_w_max": max((r[3] for r in inside), default=None),
+                "reasons": reasons, "samples": len(inside), "scope": scope}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -306,9 +313,12 @@ def run_measured(args):
     sampler = ClockSampler(r.local)
     if r.rank == 0:
         sampler.start()
+        time.sleep(0.5)  # let the sampler come up before the timed region
+    t_begin = time.time()
     seconds = r.time_steps(sets, args.op, max(args.warmup, 3), args.steps)
+    t_end = time.time()
     launches = r.launches
-    clocks = sampler.stop() if r.rank == 0 else None
+    clocks = sampler.stop((t_begin, t_end)) if r.rank == 0 else None
     e2e_seconds, h2d, d2h = r.time_e2e(sets, numel, dtype, args.op, max(args.warmup // 2, 3), max(args.steps // 4, 5))
     e2e_steps = max(args.steps // 4, 5)
     info = r.comm.last_call() if r.comm is not None else {"algo": args.impl}

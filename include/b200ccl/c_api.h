@@ -72,6 +72,18 @@ int b2_comm_last_call(const b2_comm* comm, int out[6]);
 int b2_comm_alloc_symmetric(b2_comm* comm, size_t bytes, void** ptrs);
 int b2_comm_free_symmetric(b2_comm* comm, void* const* ptrs);
 
+/* Planner (pure function, no GPU needed): out = {algo, grid, stage_in, stage_out, gather_mode}.
+ * flags bits: 1 wide, 2 peers_read_input, 4 peers_write_output, 8 input_multicast,
+ * 16 output_multicast, 32 in_place, 64 ring_only. Returns 2 with a message when impossible. */
+int b2_make_plan(int collective, int dtype, int redop, int nranks, size_t count, unsigned flags, int forced_algo,
+                 int out[5]);
+
+/* CPU ring simulator (no GPU needed). cfg: {nranks, channels, redop, collective, stall_rank,
+ * stall_after_slices}; out_i: {wrong, timed_out, timeout_rank, timeout_peer, timeout_channel,
+ * slices, empty_slices}; out_d: {seconds, max_abs_error}. */
+int b2_ring_sim(const long long cfg[6], size_t count, size_t fifo_bytes, double wait_timeout_ms, long long out_i[7],
+                double out_d[2]);
+
 #ifdef __cplusplus
 }
 #endif

@@ -2,6 +2,8 @@
 
 #include "b200ccl/bootstrap.h"
 #include "b200ccl/communicator.h"
+#include "sched/plan.h"
+#include "sim/ring_sim.h"
 
 #include <cstring>
 #include <exception>
@@ -156,6 +158,59 @@ int b2_comm_free_symmetric(b2_comm* c, void* const* ptrs) {
     return guarded([&] {
         std::vector<void*> v(ptrs, ptrs + c->comm->local_rank_count());
         c->comm->free_symmetric(v);
+    });
+}
+
+int b2_make_plan(int collective, int dtype, int redop, int nranks, size_t count, unsigned flags, int forced_algo,
+                 int out[5]) {
+    return guarded([&] {
+        sched::CallShape s;
+        s.collective = static_cast<Collective>(collective);
+        s.dtype = static_cast<DType>(dtype);
+        s.redop = static_cast<RedOp>(redop);
+        s.nranks = nranks;
+        s.count = count;
+        s.wide = flags & 1u;
+        s.peers_read_input = flags & 2u;
+        s.peers_write_output = flags & 4u;
+        s.input_multicast = flags & 8u;
+        s.output_multicast = flags & 16u;
+        s.in_place = flags & 32u;
+        s.ring_only = flags & 64u;
+        const sched::Plan p = sched::make_plan(s, static_cast<Algo>(forced_algo), sched::default_tuning());
+        if (!p.error.empty()) throw std::invalid_argument(p.error);
+        out[0] = static_cast<int>(p.algo);
+        out[1] = p.grid;
+        out[2] = p.stage_in;
+        out[3] = p.stage_out;
+        out[4] = p.gather_mode;
+    });
+}
+
+int b2_ring_sim(const long long cfg[6], size_t count, size_t fifo_bytes, double wait_timeout_ms, long long out_i[7],
+                double out_d[2]) {
+    return guarded([&] {
+        sim::RingSimConfig c;
+        c.nranks = static_cast<int>(cfg[0]);
+        c.channels = static_cast<int>(cfg[1]);
+        c.redop = static_cast<RedOp>(cfg[2]);
+        c.collective = static_cast<Collective>(cfg[3]);
+        c.stall_rank = static_cast<int>(cfg[4]);
+        c.stall_after_slices = cfg[5];
+        c.count = count;
+        c.fifo_bytes = fifo_bytes;
+        c.wait_timeout_ms = wait_timeout_ms;
+        const sim::RingSimResult r = sim::run_ring_sim(c);
+        if (r.wrong < 0) throw std::invalid_argument(r.message);
+        out_i[0] = r.wrong;
+        out_i[1] = r.timed_out;
+        out_i[2] = r.timeout_rank;
+        out_i[3] = r.timeout_peer;
+        out_i[4] = r.timeout_channel;
+        out_i[5] = static_cast<long long>(r.slices);
+        out_i[6] = static_cast<long long>(r.empty_slices);
+        out_d[0] = r.seconds;
+        out_d[1] = r.max_abs_error;
     });
 }
 

@@ -172,14 +172,18 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
     topo_ = topo::discover(config.devices);
     resolve_transport(config);
 
-    mem::GroupDesc group;
-    group.nranks = nranks_;
-    group.bootstrap = bootstrap_;
-    group.want_multicast = config.enable_nvls && resolved_ == TransportKind::P2p;
-    group.loopback = loopback_;
-    for (const auto& l : local_) group.local.push_back({l.grank, l.device});
-    alloc_.reset(new mem::SymmetricAllocator(group));
-    ctrl_ = alloc_->allocate(sizeof(dev::ControlBlock), "control");
+    // Peer-mapped memory exists for every transport except SHM, whose point is to work
+    // without peer access (everything it shares lives in mapped host memory).
+    if (resolved_ != TransportKind::Shm) {
+        mem::GroupDesc group;
+        group.nranks = nranks_;
+        group.bootstrap = bootstrap_;
+        group.want_multicast = config.enable_nvls && resolved_ == TransportKind::P2p;
+        group.loopback = loopback_;
+        for (const auto& l : local_) group.local.push_back({l.grank, l.device});
+        alloc_.reset(new mem::SymmetricAllocator(group));
+        ctrl_ = alloc_->allocate(sizeof(dev::ControlBlock), "control");
+    }
 
     for (auto& l : local_) {
         DeviceGuard guard(l.device);
@@ -290,6 +294,7 @@ Located Communicator::Impl::locate(const void* p, std::size_t bytes, int grank) 
 
 std::vector<void*> Communicator::Impl::alloc_symmetric(std::size_t bytes) {
     check_async_error();
+    if (!alloc_) throw std::runtime_error("symmetric memory is not available with transport shm");
     auto region = alloc_->allocate(bytes, "user");
     std::vector<void*> out;
     for (const auto& l : local_) out.push_back(region->rank_ptr(l.grank));
@@ -446,7 +451,7 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
     shape.peers_write_output = direct_peer_pointers() || out_sym;
     shape.input_multicast = in_sym && heap_[in_loc[0].region]->multicast_ptr() != nullptr;
     shape.output_multicast = out_sym && heap_[out_loc[0].region]->multicast_ptr() != nullptr;
-    shape.ring_only = resolved_ != TransportKind::P2p;
+    shape.ring_only = resolved_ != TransportKind::P2p;  // shm, socket, rdma: only the ring crosses those edges
     shape.max_ctas = tuning_.max_ctas;
     const sched::Plan plan = sched::make_plan(shape, forced_algo_, tuning_);
     if (!plan.error.empty()) throw std::invalid_argument(std::string(collective_name(collective)) + ": " + plan.error);
@@ -469,9 +474,10 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
             rc.timeout_ns = timeout_ns_;
             rc.use_host_fifo = resolved_ == TransportKind::Shm;
             rc.loopback = loopback_;
+            if (resolved_ == TransportKind::Socket || resolved_ == TransportKind::Rdma) rc.net_kind = resolved_;
             for (const auto& l : local_) rc.local.push_back({l.grank, l.device});
             for (const auto& l : local_) rc.status.push_back(l.status);
-            ring_.reset(new RingEngine(rc, *alloc_, *ctrl_, bootstrap_));
+            ring_.reset(new RingEngine(rc, alloc_.get(), ctrl_.get(), bootstrap_));
         }
         try {
             for (std::size_t i = 0; i < local_.size(); ++i) {
@@ -643,9 +649,12 @@ std::string Communicator::Impl::describe() const {
     os << "b200ccl communicator: " << nranks_ << " ranks, " << local_.size() << " local"
        << (loopback_ ? " (loopback emulation)" : "") << (multiprocess_ ? " (multi-process)" : "") << "\n";
     os << "transport: requested " << transport_name(requested_) << ", resolved " << transport_name(resolved_) << "\n";
-    os << "memory: " << (alloc_->uses_vmm() ? "virtual memory management" : "cudaMalloc + peer access")
-       << "; NVLS multicast " << (alloc_->multicast_supported() ? "available" : ("unavailable (" + alloc_->multicast_reason() + ")"))
-       << "\n";
+    if (alloc_)
+        os << "memory: " << (alloc_->uses_vmm() ? "virtual memory management" : "cudaMalloc + peer access")
+           << "; NVLS multicast "
+           << (alloc_->multicast_supported() ? "available" : ("unavailable (" + alloc_->multicast_reason() + ")")) << "\n";
+    else
+        os << "memory: mapped host memory only (shm)\n";
     for (const auto& l : local_) os << "rank " << l.grank << ": device " << l.device << "\n";
     os << topo_.text;
     // Every rank reaches every other rank over the same kind of edge.

@@ -24,13 +24,17 @@ struct RingEngineConfig {
     unsigned long long timeout_ns = 0;
     bool use_host_fifo = false;  // SHM transport: FIFOs and counters in mapped pinned host memory
     bool loopback = false;
+    // Socket or Rdma: ring edges that leave this process run over that network transport
+    // (host FIFO + proxy threads); Auto: every edge is local or peer-mapped.
+    TransportKind net_kind = TransportKind::Auto;
     std::vector<mem::LocalRankDesc> local;
     std::vector<dev::Status*> status;  // one per local rank
 };
 
 class RingEngine {
 public:
-    RingEngine(const RingEngineConfig& config, mem::SymmetricAllocator& alloc, mem::SymmetricRegion& ctrl,
+    // `alloc` and `ctrl` may be null when use_host_fifo is set (no peer-mapped memory exists then).
+    RingEngine(const RingEngineConfig& config, mem::SymmetricAllocator* alloc, const mem::SymmetricRegion* ctrl,
                Bootstrap* bootstrap);
     ~RingEngine();
     void launch(Collective collective, const CollectiveArgs& args);

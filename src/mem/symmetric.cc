@@ -185,7 +185,7 @@ std::unique_ptr<SymmetricRegion> SymmetricAllocator::allocate_vmm(std::size_t by
     if (multicast_) {
         CUmulticastObjectProp mp = multicast_prop(n, align_up(bytes, gran));
         std::size_t mg = 0;
-        if (a.MulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_RECOMMENDED) == CUDA_SUCCESS && mg)
+        if (a.MulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_MINIMUM) == CUDA_SUCCESS && mg)
             gran = std::max(gran, mg);
     }
     const std::size_t size = align_up(bytes, gran);
@@ -323,7 +323,7 @@ void SymmetricAllocator::try_bind_multicast(SymmetricRegion& r, const char* labe
     {
         CUmulticastObjectProp mp = multicast_prop(n, size);
         std::size_t mg = 0;
-        if (a.MulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_RECOMMENDED) == CUDA_SUCCESS && mg)
+        if (a.MulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_MINIMUM) == CUDA_SUCCESS && mg)
             gran = mg;
     }
     CUresult st = a.MemAddressReserve(&va, size, gran, 0, 0);

@@ -46,7 +46,8 @@ int grid_for(std::size_t bytes_this_rank_handles, const Tuning& t, int cap) {
 }
 
 bool nvls_usable(const CallShape& s) {
-    if (!s.wide || s.nranks < 2) return false;
+    // At two ranks the switch saves no traffic over direct peer access and measured slower.
+    if (!s.wide || s.nranks < 3) return false;
     switch (s.collective) {
         case Collective::AllReduce:
             return (s.redop == RedOp::Sum || s.redop == RedOp::Avg) && s.input_multicast && s.output_multicast;
