@@ -223,9 +223,11 @@ void Communicator::Impl::resolve_transport(const CommunicatorConfig& config) {
             break;
         case TransportKind::Socket:
         case TransportKind::Rdma:
-            if (!multiprocess_)
-                throw std::invalid_argument(std::string("transport ") + transport_name(requested_) +
-                                            " needs a multi-process communicator (bootstrap)");
+            // Multi-process: the ring edges between processes use the network transport. Single
+            // process: every ring edge loops through it (TCP on the loopback interface, or the
+            // in-process verbs backend), which tests the whole path on one host. Edges inside a
+            // process still need peer access for the FIFOs of local edges.
+            if (!peers_ok(&why)) throw std::runtime_error(std::string("transport ") + transport_name(requested_) + ": " + why);
             resolved_ = requested_;
             break;
         default: throw std::invalid_argument("bad transport");

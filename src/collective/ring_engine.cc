@@ -83,6 +83,7 @@ RingEngine::RingEngine(const RingEngineConfig& config, mem::SymmetricAllocator* 
         nc.channels = C;
         nc.fifo_bytes = s.fifo_bytes;
         nc.local = config.local;
+        nc.all_edges = bootstrap == nullptr;  // single process: every edge loops through the transport
         s.net = transport::create_net_edges(nc, bootstrap);
     }
     if (env::get_bool("B200CCL_RING_TURNAROUND", false)) s.stats.reset(config.local.size() * C);

@@ -31,6 +31,10 @@ struct NetEdgeConfig {
     int channels = 0;
     std::size_t fifo_bytes = 0;
     std::vector<mem::LocalRankDesc> local;
+    // Every ring edge goes over the network transport, also those between two ranks of this
+    // process (loopback connections). Used when a single-process communicator asks for socket or
+    // rdma: it exercises the whole kernel → proxy → wire → proxy → kernel path on one host.
+    bool all_edges = false;
 };
 
 class NetEdgeSet {
@@ -47,6 +51,7 @@ public:
 
 // Connects every cross-process ring edge (lower bootstrap rank connects, higher accepts) and
 // builds the proxies. Throws on every process if any process failed (error consensus).
+// `bootstrap` may be null for a single-process communicator (then all_edges must be set).
 std::unique_ptr<NetEdgeSet> create_net_edges(const NetEdgeConfig& config, Bootstrap* bootstrap);
 
 }  // namespace b200ccl::transport

@@ -37,12 +37,17 @@ public:
         const int n = cfg.nranks, C = cfg.channels;
         // Which process owns which rank.
         struct Range { int first, count; };
+        const int nproc = bs ? bs->size() : 1, me = bs ? bs->rank() : 0;
         Range mine{cfg.local.front().global_rank, static_cast<int>(cfg.local.size())};
-        std::vector<Range> ranges(bs->size());
-        bs->allgather(&mine, ranges.data(), sizeof(Range));
+        std::vector<Range> ranges(nproc);
+        if (bs) bs->allgather(&mine, ranges.data(), sizeof(Range));
+        else ranges[0] = mine;
         std::vector<int> owner(n, -1);
-        for (int p = 0; p < bs->size(); ++p)
+        for (int p = 0; p < nproc; ++p)
             for (int k = 0; k < ranges[p].count; ++k) owner[ranges[p].first + k] = p;
+        // The process of the sending rank opens the connection when its bootstrap rank is not
+        // higher than the receiver's (equal = loopback inside one process); else the receiver's does.
+        auto sender_connects = [&](int src, int dst) { return owner[src] <= owner[dst]; };
 
         // Listener with consensus.
         std::string err;
@@ -51,10 +56,11 @@ public:
         } catch (const std::exception& e) {
             err = std::string("socket listener setup failed: ") + e.what();
         }
-        const std::string all_err = bs->error_consensus(err);
+        const std::string all_err = bs ? bs->error_consensus(err) : err;
         if (!all_err.empty()) throw std::runtime_error("socket listener setup failed on " + all_err);
-        std::vector<SocketAddress> addrs(bs->size());
-        bs->allgather(&listener_.address(), addrs.data(), sizeof(SocketAddress));
+        std::vector<SocketAddress> addrs(nproc);
+        if (bs) bs->allgather(&listener_.address(), addrs.data(), sizeof(SocketAddress));
+        else addrs[0] = listener_.address();
 
         // Halves of this process.
         const std::size_t step_bytes = cfg.fifo_bytes / ring::kFifoSteps;
@@ -76,23 +82,25 @@ public:
         std::set<std::tuple<int, int, int>> expected;  // (src, dst, channel) of connections to accept
         for (const auto& l : cfg.local) {
             const int r = l.global_rank, next = (r + 1) % n, prev = (r + n - 1) % n;
-            if (owner[next] != bs->rank())
+            if (cfg.all_edges || owner[next] != me)
                 for (int c = 0; c < C; ++c) send_[{r, c}] = make_half(r, next, c, l.device);
-            if (owner[prev] != bs->rank())
+            if (cfg.all_edges || owner[prev] != me)
                 for (int c = 0; c < C; ++c) recv_[{r, c}] = make_half(prev, r, c, l.device);
         }
         // Connect or accept, per edge and channel.
         const int timeout_ms = 30000;
         for (auto& kv : send_) {
             Half& h = *kv.second;
-            const int peer = owner[h.id.destination_rank];
-            if (bs->rank() < peer) h.connection = connect_with_hello(addrs[peer], h.id.channel, h.id.source_rank, h.id.destination_rank, timeout_ms);
+            if (sender_connects(h.id.source_rank, h.id.destination_rank))
+                h.connection = connect_with_hello(addrs[owner[h.id.destination_rank]], h.id.channel, h.id.source_rank,
+                                                  h.id.destination_rank, timeout_ms);
             else { expected.insert({h.id.source_rank, h.id.destination_rank, h.id.channel}); ++expected_accepts; }
         }
         for (auto& kv : recv_) {
             Half& h = *kv.second;
-            const int peer = owner[h.id.source_rank];
-            if (bs->rank() < peer) h.connection = connect_with_hello(addrs[peer], h.id.channel, h.id.source_rank, h.id.destination_rank, timeout_ms);
+            if (!sender_connects(h.id.source_rank, h.id.destination_rank))
+                h.connection = connect_with_hello(addrs[owner[h.id.source_rank]], h.id.channel, h.id.source_rank,
+                                                  h.id.destination_rank, timeout_ms);
             else { expected.insert({h.id.source_rank, h.id.destination_rank, h.id.channel}); ++expected_accepts; }
         }
         std::string accept_err;
@@ -107,12 +115,14 @@ public:
                                              " destination=" + std::to_string(hello.destination_rank) + " channel=" +
                                              std::to_string(hello.channel));
                 expected.erase(key);
+                // The accepting half is the one that did not connect.
                 Half* h = nullptr;
-                auto s = send_.find({static_cast<int>(hello.source_rank), static_cast<int>(hello.channel)});
-                if (s != send_.end() && s->second->id.destination_rank == static_cast<int>(hello.destination_rank)) h = s->second.get();
-                if (!h) {
+                if (sender_connects(static_cast<int>(hello.source_rank), static_cast<int>(hello.destination_rank))) {
                     auto r = recv_.find({static_cast<int>(hello.destination_rank), static_cast<int>(hello.channel)});
                     if (r != recv_.end()) h = r->second.get();
+                } else {
+                    auto s = send_.find({static_cast<int>(hello.source_rank), static_cast<int>(hello.channel)});
+                    if (s != send_.end()) h = s->second.get();
                 }
                 if (!h) throw std::runtime_error("socket hello matches no local edge");
                 h->connection = std::move(got.first);
@@ -120,7 +130,7 @@ public:
         } catch (const std::exception& e) {
             accept_err = e.what();
         }
-        const std::string all_accept = bs->error_consensus(accept_err);
+        const std::string all_accept = bs ? bs->error_consensus(accept_err) : accept_err;
         if (!all_accept.empty()) throw std::runtime_error("socket edge setup failed on " + all_accept);
 
         // Proxies.
@@ -155,7 +165,7 @@ public:
     void start() override {
         // Receivers are up before any sender may write (communicator.cu:749-784 of the reference).
         for (auto& p : recv_proxies_) p->start();
-        bs_->barrier();
+        if (bs_) bs_->barrier();
         for (auto& p : send_proxies_) p->start();
     }
 
