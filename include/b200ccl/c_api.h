@@ -84,6 +84,15 @@ int b2_make_plan(int collective, int dtype, int redop, int nranks, size_t count,
 int b2_ring_sim(const long long cfg[6], size_t count, size_t fifo_bytes, double wait_timeout_ms, long long out_i[7],
                 double out_d[2]);
 
+/* Single-GPU self-tests of the signalling primitives (bounded; they cannot hang the device).
+ * kind 0: a wait on a flag nothing sets must time out; kind 1: the host raises the abort word
+ * while a kernel waits. out = {wait_ok, status_code, where, abort_raised}; *waited_ms as measured
+ * on the device. */
+int b2_selftest_wait(int kind, int device, double timeout_ms, int out[4], double* waited_ms);
+/* A kernel writes a payload then releases a counter in mapped host memory; the host acquires the
+ * counter and must see the payload. *ok = 1 when every round held. */
+int b2_selftest_publication(int device, int rounds, int* ok);
+
 #ifdef __cplusplus
 }
 #endif

@@ -2,6 +2,7 @@
 
 #include "b200ccl/bootstrap.h"
 #include "b200ccl/communicator.h"
+#include "kernels/sm100/selftest.h"
 #include "sched/plan.h"
 #include "sim/ring_sim.h"
 
@@ -212,6 +213,22 @@ int b2_ring_sim(const long long cfg[6], size_t count, size_t fifo_bytes, double 
         out_d[0] = r.seconds;
         out_d[1] = r.max_abs_error;
     });
+}
+
+int b2_selftest_wait(int kind, int device, double timeout_ms, int out[4], double* waited_ms) {
+    return guarded([&] {
+        const kernels::SelfTestResult r = kind == 0 ? kernels::selftest_wait_timeout(device, timeout_ms)
+                                                    : kernels::selftest_abort(device, timeout_ms);
+        out[0] = r.wait_ok;
+        out[1] = static_cast<int>(r.status_code);
+        out[2] = static_cast<int>(r.where);
+        out[3] = r.abort_raised ? 1 : 0;
+        *waited_ms = r.waited_ms;
+    });
+}
+
+int b2_selftest_publication(int device, int rounds, int* ok) {
+    return guarded([&] { *ok = kernels::selftest_publication(device, rounds) ? 1 : 0; });
 }
 
 }  // extern "C"

@@ -1,0 +1,103 @@
+"""Worker for the multi-process GPU tests (one process per GPU). Modes:
+collectives — all_reduce / reduce_scatter / all_gather on plain and symmetric tensors, all dtypes;
+socket      — the same ring over TCP proxies between the processes;
+departure   — rank 1 leaves between steps (its kernels done, communicator closed); rank 0's next
+              collective must end with a timeout status from its bounded wait, not hang."""
+import os
+import sys
+import time
+
+import torch
+
+import nano_nccl_b200 as nn
+
+
+def expected_sum(world, numel, dtype, seed_base):
+    acc = torch.zeros(numel, dtype=torch.float32, device="cuda")
+    for r in range(world):
+        gen = torch.Generator(device="cuda").manual_seed(seed_base + r)
+        acc += torch.randn(numel, device="cuda", generator=gen).to(dtype).float()
+    return acc
+
+
+def my_input(rank, numel, dtype, seed_base):
+    gen = torch.Generator(device="cuda").manual_seed(seed_base + rank)
+    return torch.randn(numel, device="cuda", generator=gen).to(dtype)
+
+
+def main():
+    mode = sys.argv[1]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(rank)
+    kw = {"wait_timeout_ms": 1500 if mode == "departure" else 5000}
+    if mode == "socket":
+        kw.update(transport="socket", channels=2)
+    comm = nn.Communicator.from_env(**kw)
+    tol = {torch.float32: 1e-5, torch.float16: 1e-2, torch.bfloat16: 1e-1}
+
+    if mode in ("collectives", "socket"):
+        dtypes = [torch.float32, torch.bfloat16] if mode == "socket" else list(tol)
+        for dtype in dtypes:
+            for numel in (64, 8 * 12501, 1 << 21):
+                x = my_input(rank, numel, dtype, 100)
+                out = torch.empty_like(x)
+                comm.all_reduce(out, x, op="sum")
+                torch.cuda.synchronize()
+                comm.check_async_error()
+                ref = expected_sum(world, numel, dtype, 100)
+                assert (out.float() - ref).abs().max().item() <= tol[dtype] * (2 if dtype != torch.float32 else 1), (dtype, numel, comm.last_call())
+                if mode == "collectives":
+                    sx, so = comm.empty(numel, dtype), comm.empty(numel, dtype)
+                    sx.copy_(x)
+                    comm.all_reduce(so, sx, op="avg")
+                    torch.cuda.synchronize()
+                    comm.check_async_error()
+                    assert not comm.last_call()["staged_in"]
+                    assert (so.float() - ref / world).abs().max().item() <= tol[dtype], (dtype, numel, comm.last_call())
+                    comm.all_reduce(sx, op="sum")  # in place
+                    torch.cuda.synchronize()
+                    assert (sx.float() - ref).abs().max().item() <= tol[dtype] * 2
+                if numel % world == 0:
+                    blk = numel // world
+                    rs = torch.empty(blk, device="cuda", dtype=dtype)
+                    comm.reduce_scatter(rs, x, op="sum")
+                    ag = torch.empty(numel * world, device="cuda", dtype=dtype)
+                    comm.all_gather(ag, x)
+                    torch.cuda.synchronize()
+                    comm.check_async_error()
+                    assert (rs.float() - ref[rank * blk:(rank + 1) * blk]).abs().max().item() <= tol[dtype] * 2
+                    for r in range(world):
+                        assert torch.equal(ag[r * numel:(r + 1) * numel], my_input(r, numel, dtype, 100))
+        print(f"rank {rank}: nvls={comm.nvls} transport={comm.transport} last={comm.last_call()}")
+    elif mode == "departure":
+        x = my_input(rank, 4096, torch.float32, 5)
+        out = torch.empty_like(x)
+        comm.all_reduce(out, x)           # step 1: both ranks take part
+        torch.cuda.synchronize()
+        comm.check_async_error()
+        if rank == 1:
+            comm.close()                  # leaves between steps, nothing of its own in flight
+            print("rank 1 left")
+            print("WORKER OK")
+            return
+        time.sleep(1.0)
+        comm.all_reduce(out, x)           # step 2: the peer is gone
+        torch.cuda.synchronize()          # returns: the wait is bounded
+        try:
+            comm.check_async_error()
+            raise SystemExit("expected a timeout error")
+        except nn.B200CclError as e:
+            assert "timed out" in str(e) and "rank 1" in str(e), str(e)
+            print("detected:", e)
+        try:
+            comm.all_reduce(out, x)       # a failed communicator rejects new work
+            raise SystemExit("expected rejection")
+        except nn.B200CclError:
+            pass
+        assert torch.ones(8, device="cuda").sum().item() == 8  # the context is still usable
+    comm.close()
+    print("WORKER OK")
+
+
+if __name__ == "__main__":
+    main()
