@@ -75,6 +75,7 @@ class Communicator:
         self.local_ranks = lib.b2_comm_local_ranks(self._handle)
         self.world_size = lib.b2_comm_global_ranks(self._handle)
         self.rank = lib.b2_comm_first_rank(self._handle)
+        self._one = ((ctypes.c_void_p * 1)(), (ctypes.c_void_p * 1)(), (ctypes.c_void_p * 1)())
 
     @classmethod
     def from_env(cls, port=None, **kw):
@@ -140,9 +141,27 @@ class Communicator:
 
     # -- collectives -----------------------------------------------------------------------------
     def _run(self, coll, outs, inps, op, streams, count, in_place=False):
-        single = isinstance(inps, torch.Tensor)
-        if single:
-            inps, outs = [inps], [outs]
+        if isinstance(inps, torch.Tensor):
+            # Fast path: one local rank, one tensor each way.
+            if self.local_ranks != 1:
+                raise ValueError(f"need one tensor per local rank ({self.local_ranks})")
+            dtype = inps.dtype
+            code = _DTYPES.get(dtype)
+            if code is None:
+                raise ValueError(f"unsupported dtype {dtype}")
+            if not (inps.is_cuda and outs.is_cuda and inps.is_contiguous() and outs.is_contiguous() and outs.dtype == dtype):
+                raise ValueError("tensors must be contiguous CUDA tensors of one dtype")
+            if streams is None:
+                sp = torch.cuda.current_stream(inps.device).cuda_stream
+            else:
+                s0 = streams[0] if isinstance(streams, (list, tuple)) else streams
+                sp = s0.cuda_stream if hasattr(s0, "cuda_stream") else int(s0)
+            a = self._one
+            a[0][0], a[1][0], a[2][0] = inps.data_ptr(), outs.data_ptr(), sp
+            rc = self._lib.b2_collective(self._handle, _COLL[coll], a[0], a[1], a[2], count, code, _OPS[op], 1 if in_place else 0)
+            if rc != 0:
+                _lib.check(rc)
+            return
         if len(inps) != self.local_ranks or len(outs) != self.local_ranks:
             raise ValueError(f"need one tensor per local rank ({self.local_ranks})")
         dtype = inps[0].dtype
@@ -152,11 +171,9 @@ class Communicator:
             if not t.is_cuda or not t.is_contiguous() or t.dtype != dtype:
                 raise ValueError("tensors must be contiguous CUDA tensors of one dtype")
         if streams is None:
-            streams = []
-            for t in inps:
-                streams.append(torch.cuda.current_stream(t.device).cuda_stream)
+            streams = [torch.cuda.current_stream(t.device).cuda_stream for t in inps]
         elif not isinstance(streams, (list, tuple)):
-            streams = [streams]
+            streams = [streams] * len(inps)
         streams = [s.cuda_stream if hasattr(s, "cuda_stream") else int(s) for s in streams]
         n = self.local_ranks
         send = (ctypes.c_void_p * n)(*[t.data_ptr() for t in inps])

@@ -34,7 +34,7 @@ __device__ __forceinline__ const A& select_args(const LoopPack<A>& all) { return
 
 template <int N>
 struct UnrollFor {
-    static constexpr int value = N == 0 ? 1 : (N >= 8 ? 1 : (N >= 4 ? 2 : 4));
+    static constexpr int value = N == 0 ? 1 : (N >= 8 ? 1 : (N >= 4 ? 2 : (N >= 2 ? 4 : 8)));
 };
 
 // One template for one-shot / two-shot / ReduceScatter / NVLS; the differences are data:
@@ -277,6 +277,7 @@ cudaError_t launch_reduce_n(int nranks, const ParamT& param, const LaunchConfig&
         return launch(reduce_kernel<T, Op, 0, PackT, false, ParamT>, param, cfg);
     } else {
         switch (nranks) {
+            case 1: return launch(reduce_kernel<T, Op, 1, PackT, false, ParamT>, param, cfg);
             case 2: return launch(reduce_kernel<T, Op, 2, PackT, false, ParamT>, param, cfg);
             case 4: return launch(reduce_kernel<T, Op, 4, PackT, false, ParamT>, param, cfg);
             case 8: return launch(reduce_kernel<T, Op, 8, PackT, false, ParamT>, param, cfg);

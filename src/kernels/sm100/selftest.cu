@@ -125,6 +125,7 @@ bool selftest_publication(int device, int rounds) {
     unsigned long long* step = nullptr;
     B2_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&payload), kWords * sizeof(unsigned int), cudaHostAllocMapped));
     B2_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&step), sizeof(unsigned long long), cudaHostAllocMapped));
+    *step = 0;  // cudaHostAlloc does not clear memory
     cudaStream_t stream;
     B2_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
     bool good = true;

@@ -74,7 +74,7 @@ Plan make_plan(const CallShape& s, Algo forced, const Tuning& t) {
     }
     if (s.nranks == 1) {
         p.algo = Algo::OneShot;  // degenerates to a local copy (with the avg scale of 1)
-        p.grid = grid_for(bytes, t, cap);
+        p.grid = grid_for(bytes, t, 148);  // nothing to share the GPU with: one CTA per SM
         p.gather_mode = 1;
         return p;
     }
