@@ -20,12 +20,9 @@ sampled with nvidia-smi during the timed region.
 import argparse
 import json
 import os
-import re
 import socket
 import subprocess
 import sys
-import tempfile
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -54,67 +51,7 @@ def parse_args():
     return ap.parse_args()
 
 
-# ---------------------------------------------------------------------------------------------
-# clocks
-
-class ClockSampler:
-    """Runs `nvidia-smi -lms 200` while the timed region executes and summarises one GPU's samples."""
-
-    QUERY = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index):
-        self.gpu_index = gpu_index
-        self.proc = None
-        self.path = None
-
-    def start(self):
-        try:
-            fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
-            os.close(fd)
-            self.out = open(self.path, "w")
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50"],
-                stdout=self.out, stderr=subprocess.DEVNULL)
-        except Exception:
-            self.proc = None
-
-    def stop(self, window=None):
-        """Summarises the samples of this GPU; `window` = (t0, t1) wall-clock seconds keeps only samples
-        taken inside it (falls back to all samples when none fall inside)."""
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        self.out.close()
-        import datetime
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        rows = []
-        with open(self.path) as f:
-            for line in f:
-                parts = [p.strip() for p in line.split(",")]
-                if len(parts) < 10 or parts[1] != str(self.gpu_index):
-                    continue
-                try:
-                    ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
-                    rows.append((ts, float(parts[2]), float(parts[3]), float(parts[4]),
-                                 [n for n, v in zip(names, parts[6:10]) if v.lower().startswith("active")]))
-                except ValueError:
-                    continue
-        os.unlink(self.path)
-        inside = [r for r in rows if window and window[0] <= r[0] <= window[1]]
-        scope = "timed region"
-        if not inside:
-            inside, scope = rows, "whole run (no sample fell inside the timed region)"
-        clocks = sorted(r[1] for r in inside)
-        reasons = sorted({n for r in inside for n in r[4]})
-        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None,
-                "sm_max_mhz": max((r[2] for r in inside), default=None),
-                "power_w_max": max((r[3] for r in inside), default=None),
-                "reasons": reasons, "samples": len(inside), "scope": scope}
+from nano_nccl_b200.utils.clocks import ClockSampler  # noqa: E402  (reads clocks only)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -313,7 +250,7 @@ def run_measured(args):
     sampler = ClockSampler(r.local)
     if r.rank == 0:
         sampler.start()
-        time.sleep(0.5)  # let the sampler come up before the timed region
+        time.sleep(0.05)  # let the sampler come up before the timed region
     t_begin = time.time()
     seconds = r.time_steps(sets, args.op, max(args.warmup, 3), args.steps)
     t_end = time.time()

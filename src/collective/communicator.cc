@@ -65,6 +65,7 @@ private:
         dev::Status* status = nullptr;  // pinned, mapped
         cudaEvent_t done = nullptr;
         bool launched = false;
+        cudaStream_t last_stream = nullptr;
     };
 
     void resolve_transport(const CommunicatorConfig& config);
@@ -318,13 +319,17 @@ void Communicator::Impl::free_symmetric(const std::vector<void*>& ptrs) {
     throw std::invalid_argument("free_symmetric: pointer was not returned by alloc_symmetric");
 }
 
+// Successive collectives of one rank run in issue order. On the same stream that is stream order
+// (which also keeps a stream capture free of dependencies on events recorded outside it); on a
+// different stream the new launch waits for the previous one's completion event.
 void Communicator::Impl::wait_previous(Local& l, cudaStream_t stream) {
-    if (l.launched) B2_CUDA(cudaStreamWaitEvent(stream, l.done, 0));
+    if (l.launched && l.last_stream != stream) B2_CUDA(cudaStreamWaitEvent(stream, l.done, 0));
 }
 
 void Communicator::Impl::record_done(Local& l, cudaStream_t stream) {
     B2_CUDA(cudaEventRecord(l.done, stream));
     l.launched = true;
+    l.last_stream = stream;
 }
 
 void Communicator::Impl::fill_common(dev::CollArgs& a, const Local& l) const {
