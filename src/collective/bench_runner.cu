@@ -2,6 +2,7 @@
 #include "b200ccl/bench.h"
 
 #include "b200ccl/traits.h"
+#include "collective/bench_profiling.h"
 #include "core/check.h"
 #include "core/datagen.h"
 
@@ -235,7 +236,15 @@ int run_collective_bench(const BenchConfig& config, std::vector<BenchResult>* re
                 DeviceGuard guard(ranks[r].device);
                 B2_CUDA(cudaEventRecord(ranks[r].start, ranks[r].stream));
             }
-            for (int i = 0; i < config.iters; ++i) issue(i % sets);
+            {
+                // Capture window and ranges cover the measured batch only (no-ops in normal builds).
+                ProfilerSession session;
+                NvtxRange size_range(bench_range_name(collective_name(coll), count * esz));
+                for (int i = 0; i < config.iters; ++i) {
+                    NvtxRange iter_range(bench_range_name(collective_name(coll), count * esz, i));
+                    issue(i % sets);
+                }
+            }
             for (int r = 0; r < record_ranks; ++r) {
                 DeviceGuard guard(ranks[r].device);
                 B2_CUDA(cudaEventRecord(ranks[r].stop, ranks[r].stream));
