@@ -22,6 +22,14 @@ struct b2_bootstrap {
 
 namespace {
 thread_local std::string g_error;
+}  // namespace
+
+namespace b200ccl::kernels {
+// Lets entry points defined beside the kernels report through b2_last_error().
+void set_last_error_message(const std::string& message) { g_error = message; }
+}  // namespace b200ccl::kernels
+
+namespace {
 
 template <typename F>
 int guarded(F&& f) {

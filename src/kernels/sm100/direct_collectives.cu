@@ -347,3 +347,125 @@ cudaError_t launch_gather(const GatherArgs* args, const LaunchConfig& cfg) {
 }
 
 }  // namespace b200ccl::kernels
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free single-GPU all-reduce (declaration and contract: kernels/sm100/no_alloc.h).
+// Same kernel as the communicator's single-GPU emulation; the control blocks live in the array
+// below instead of in memory obtained from the driver.
+
+#include "kernels/sm100/no_alloc.h"
+
+#include <cstdint>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+namespace b200ccl::kernels {
+// Message of the calling thread's last failure, shared with the C interface (b2_last_error).
+void set_last_error_message(const std::string& message);
+}  // namespace b200ccl::kernels
+
+namespace {
+
+// The scratch: one control block per emulated rank. In host code this name is only a stand-in
+// for the device object; its device address is obtained once per device with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_no_alloc_scratch[B2_NO_ALLOC_MAX_RANKS * sizeof(b200ccl::dev::ControlBlock)];
+
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_no_alloc_mutex;
+void* g_no_alloc_address[kNoAllocMaxDevices] = {nullptr};  // device address of the array, per device ordinal
+
+// Device address of the scratch array on the current device (resolved on first use).
+cudaError_t no_alloc_scratch_address(void** out) {
+    int device = 0;
+    cudaError_t st = cudaGetDevice(&device);
+    if (st != cudaSuccess) return st;
+    if (device < 0 || device >= kNoAllocMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
+    if (g_no_alloc_address[device] == nullptr) {
+        void* ptr = nullptr;
+        st = cudaGetSymbolAddress(&ptr, g_no_alloc_scratch);
+        if (st != cudaSuccess) return st;
+        g_no_alloc_address[device] = ptr;
+    }
+    *out = g_no_alloc_address[device];
+    return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" int b2_local_all_reduce_no_alloc(const void* const* inputs, void* const* outputs, int nranks, size_t count,
+                                            int dtype, int redop, void* stream, void* status_record) {
+    using namespace b200ccl;
+    using namespace b200ccl::dev;
+    auto reject = [](const std::string& why) {
+        kernels::set_last_error_message("b2_local_all_reduce_no_alloc: " + why);
+        return 2;
+    };
+    if (nranks < 1 || nranks > B2_NO_ALLOC_MAX_RANKS)
+        return reject("nranks = " + std::to_string(nranks) + " is outside 1.." + std::to_string(B2_NO_ALLOC_MAX_RANKS) +
+                      " (the fixed scratch array holds " + std::to_string(B2_NO_ALLOC_MAX_RANKS) + " control blocks)");
+    if (count == 0) return reject("count must be positive");
+    if (dtype < 0 || dtype > 2) return reject("unsupported dtype");
+    if (redop < 0 || redop > 3) return reject("unknown reduction operator");
+    if (inputs == nullptr || outputs == nullptr) return reject("inputs and outputs must be non-null");
+    for (int r = 0; r < nranks; ++r) {
+        if (inputs[r] == nullptr || outputs[r] == nullptr) return reject("every buffer must be non-null");
+        for (int q = 0; q < nranks; ++q)
+            if (inputs[r] == outputs[q]) return reject("in-place operation is not supported");
+    }
+    void* scratch = nullptr;
+    cudaError_t st = no_alloc_scratch_address(&scratch);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // The array keeps the previous call's flags, epochs and abort word: start from zero.
+    if (st == cudaSuccess) st = cudaMemsetAsync(scratch, 0, sizeof(ControlBlock) * B2_NO_ALLOC_MAX_RANKS, s);
+    if (st != cudaSuccess) {
+        kernels::set_last_error_message(std::string("b2_local_all_reduce_no_alloc: ") + cudaGetErrorString(st));
+        (void)cudaGetLastError();
+        return 1;
+    }
+    const DType dt = static_cast<DType>(dtype);
+    const RedOp op = static_cast<RedOp>(redop);
+    const std::size_t esz = dtype_size(dt);
+    bool wide = (count * esz) % 16 == 0;
+    for (int r = 0; r < nranks; ++r)
+        wide = wide && ((reinterpret_cast<std::uintptr_t>(inputs[r]) | reinterpret_cast<std::uintptr_t>(outputs[r])) & 15u) == 0;
+    const std::size_t pack = wide ? 16 : esz;
+    const std::size_t bytes = count * esz;
+    const bool oneshot = bytes <= (std::size_t(256) << 10);
+    CollArgs args[B2_NO_ALLOC_MAX_RANKS];
+    for (int r = 0; r < nranks; ++r) {
+        CollArgs& a = args[r];
+        std::memset(&a, 0, sizeof(a));
+        for (int p = 0; p < nranks; ++p) {
+            a.ctrl[p] = reinterpret_cast<ControlBlock*>(static_cast<unsigned char*>(scratch) + sizeof(ControlBlock) * p);
+            a.in[p] = inputs[p];
+            a.out[p] = oneshot ? nullptr : outputs[p];
+        }
+        a.out[r] = outputs[r];
+        a.status = static_cast<Status*>(status_record);
+        a.timeout_ns = static_cast<unsigned long long>(B2_NO_ALLOC_WAIT_MS) * 1000000ull;
+        a.scale = op == RedOp::Avg ? 1.0f / static_cast<float>(nranks) : 1.0f;
+        a.rank = r;
+        a.nranks = nranks;
+        a.len = bytes / pack;
+        a.shard_mode = oneshot ? kShardWhole : kShardSplit;
+        a.store_all = oneshot ? 0 : 1;
+    }
+    kernels::LaunchConfig cfg;
+    const std::size_t per_cta = std::size_t(32) << 10;
+    const std::size_t work = oneshot ? bytes : bytes / nranks;
+    std::size_t grid = (work + per_cta - 1) / per_cta;
+    const std::size_t cap = static_cast<std::size_t>(128 / nranks > 0 ? 128 / nranks : 1);
+    cfg.grid = static_cast<int>(grid < 1 ? 1 : (grid > cap ? cap : grid));
+    cfg.block = kBlockThreads;
+    cfg.stream = s;
+    cfg.loop_ranks = nranks;
+    st = kernels::launch_reduce(dt, op, wide, false, args, cfg);
+    if (st != cudaSuccess) {
+        kernels::set_last_error_message(std::string("b2_local_all_reduce_no_alloc: launch failed: ") + cudaGetErrorString(st));
+        (void)cudaGetLastError();
+        return 1;
+    }
+    return 0;
+}
