@@ -69,4 +69,11 @@ for n in 2 4 8; do
     || { tail -40 "$WORK/ninja_$n.log"; exit 1; }
   cp "$WORK/b$n/benchmarks/nano_nccl_all_reduce_bench" "$OUT/bin/nano_nccl_all_reduce_bench_n$n"
   echo "built $OUT/bin/nano_nccl_all_reduce_bench_n$n"
+  # Harness over the reference's public API for the end-to-end measurement (see ref_e2e_driver.cu).
+  nvcc -O3 -std=c++17 -arch=sm_100 -I"$WORK/src/include" -I"$WORK/src/src" -I"$WORK/shim" \
+    -DNANO_NCCL_NRANKS=$n -DNANO_NCCL_NCHANNELS=4 -DNANO_NCCL_BLOCK_THREADS=512 -DNANO_NCCL_FIFO_BUFF_BYTES=33554432 \
+    "$HERE/ref_e2e_driver.cu" "$WORK/b$n/src/libnano_nccl.a" "$WORK/shim/libnuma.a" \
+    -L/usr/local/cuda/lib64/stubs -lnvidia-ml -lpthread -o "$OUT/bin/ref_e2e_n$n" \
+    > "$WORK/driver_$n.log" 2>&1 || { tail -30 "$WORK/driver_$n.log"; exit 1; }
+  echo "built $OUT/bin/ref_e2e_n$n"
 done

@@ -346,42 +346,71 @@ def run_reference(args):
 
 
 def reference_measure(binary, args, n):
-    cmd = [binary, "--dtype", args.dtype, "--redop", args.op, "--transport", args.ref_transport,
-           "-b", str(args.bytes), "-e", str(args.bytes), "-f", "2", "-w", str(max(args.warmup, 3)), "-n", str(args.steps)]
+    """Runs (1) the harness baseline/ref_e2e_driver.cu built against the unmodified reference library:
+    K all_reduce calls through its public API timed with CUDA events (max over ranks), then the same
+    K steps end to end with the host-to-device input copy and a 4 KiB read-back; (2) the reference's
+    stock benchmark binary, whose own host-clock row is kept under "stock_benchmark"."""
+    warm = max(args.warmup, 3)
     sampler = ClockSampler(0)
     sampler.start()
     t0 = time.time()
+    harness = os.path.join(os.path.dirname(binary), f"ref_e2e_n{n}")
+    e2e_row = None
+    harness_note = None
+    if args.dtype == "float" and args.op == "sum" and os.path.exists(harness):
+        try:
+            proc = subprocess.run([harness, str(args.bytes), str(args.steps), str(warm), args.ref_transport],
+                                  capture_output=True, text=True, timeout=600)
+            for line in proc.stdout.splitlines():
+                if line.startswith("REF_E2E"):
+                    parts = line.split()
+                    e2e_row = {parts[k]: parts[k + 1] for k in range(1, len(parts) - 1, 2)}
+            if e2e_row is None:
+                harness_note = f"harness exit {proc.returncode}: {(proc.stderr or proc.stdout).strip()[-200:]}"
+        except subprocess.TimeoutExpired:
+            harness_note = "harness did not finish within 600 s"
+    t1 = time.time()
+    cmd = [binary, "--dtype", args.dtype, "--redop", args.op, "--transport", args.ref_transport,
+           "-b", str(args.bytes), "-e", str(args.bytes), "-f", "2", "-w", str(warm), "-n", str(args.steps)]
+    stock = None
     try:
         proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        for line in proc.stdout.splitlines():
+            parts = line.split()
+            if not line.startswith("#") and len(parts) >= 11 and parts[4].isdigit():
+                stock = {"transport": parts[3], "bytes": int(parts[4]), "time_us": float(parts[6]), "algbw_gbs": float(parts[7]),
+                         "busbw_gbs": float(parts[8]), "wrong_ranks": int(parts[9]), "timing": "host steady_clock (its stock method)"}
+        if stock is None:
+            stock = {"error": f"exit {proc.returncode}: {(proc.stderr or proc.stdout).strip()[-200:]}"}
     except subprocess.TimeoutExpired:
-        sampler.stop()
-        return {"impl": "reference", "unavailable": "reference benchmark did not finish within 600 s"}
-    wall = time.time() - t0
-    clocks = sampler.stop()
-    row = None
-    for line in proc.stdout.splitlines():
-        if line.startswith("#") or not line.strip():
-            continue
-        parts = line.split()
-        if len(parts) >= 11 and parts[4].isdigit():
-            row = parts
-    if row is None:
-        tail = (proc.stderr or proc.stdout).strip().splitlines()[-1:] or ["no output"]
-        return {"impl": "reference", "unavailable": f"reference benchmark gave no result row (exit {proc.returncode}): {tail[0][:200]}"}
-    time_us, algbw, bus, wrong = float(row[6]), float(row[7]), float(row[8]), int(row[9])
+        stock = {"error": "did not finish within 600 s"}
+    clocks = sampler.stop((t0, t1))
+    if e2e_row is None and (stock is None or "error" in stock):
+        return {"impl": "reference", "unavailable": f"reference gave no result: {harness_note}; stock: {stock}"[:300]}
+    if e2e_row is not None:
+        per_step = float(e2e_row["kernel_ms_per_step"]) / 1e3
+        e2e_step = float(e2e_row["e2e_ms_per_step"]) / 1e3
+        value = busbw(args.bytes, per_step, n)
+        e2e = {"value": round(busbw(args.bytes, e2e_step, n), 2), "unit": "GB/s", "h2d_bytes_per_step": int(e2e_row["h2d_bytes"]),
+               "d2h_bytes_per_step": int(e2e_row["d2h_bytes"]), "steps": args.steps, "ms_per_step": round(e2e_step * 1e3, 5),
+               "note": "per step and rank: pinned-host -> device copy of the whole input, Communicator::all_reduce, 4 KiB read-back"}
+        wrong, transport = int(e2e_row["wrong"]), e2e_row["transport"]
+        timing = "CUDA events on every rank's stream around K back-to-back calls, max over ranks (harness over the reference's public API)"
+    else:
+        per_step = stock["time_us"] / 1e6
+        value, e2e, wrong, transport = stock["busbw_gbs"], None, stock["wrong_ranks"], stock["transport"]
+        timing = stock["timing"]
     return {
-        "metric": "allreduce_busbw_gbs_64MiB_float_sum", "value": bus, "unit": "GB/s", "impl": "reference",
-        "n_gpus": n, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(time_us / 1e3, 5),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": round(bus / BASELINE_BUSBW, 2), "dtype": args.dtype,
-        "data": "synthetic: the reference benchmark's own arithmetic input pattern", "wrong": wrong,
+        "metric": "allreduce_busbw_gbs_64MiB_float_sum", "value": round(value, 2), "unit": "GB/s", "impl": "reference",
+        "n_gpus": n, "steps": args.steps, "warmup": warm, "ms_per_step": round(per_step * 1e3, 5),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": round(value / BASELINE_BUSBW, 2), "dtype": args.dtype,
+        "data": "synthetic: fixed arithmetic pattern per rank", "wrong": wrong,
         "config": {"model": "AllReduce (collective library; no neural model)", "collective": "all_reduce", "redop": args.op,
-                   "bytes_per_rank": int(row[4]), "global_batch": int(row[4]) * n, "seq_len": int(row[5]),
-                   "parallelism": f"allreduce{n}", "transport": row[3], "requested_transport": args.ref_transport,
-                   "binary": f"nano_nccl_all_reduce_bench built with -DNANO_NCCL_NRANKS={n} -DNANO_NCCL_CUDA_ARCH=100",
-                   "timing": "the reference's own host steady_clock around the batch (its stock method)",
-                   "l2": "single buffer pair (the reference's stock benchmark)"},
-        "clocks": clocks, "wall_seconds": round(wall, 2),
-        "e2e": None, "gpu_launches": args.steps * n,
+                   "bytes_per_rank": args.bytes, "global_batch": args.bytes * n, "seq_len": args.bytes // 4,
+                   "parallelism": f"allreduce{n}", "transport": transport, "requested_transport": args.ref_transport,
+                   "build": f"unmodified reference, -DNANO_NCCL_NRANKS={n} -DNANO_NCCL_CUDA_ARCH=100, one process driving {n} GPUs",
+                   "timing": timing, "l2": "single buffer pair of 2 x 64 MiB per GPU (the reference's FIFO traffic adds to it)"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * n, "stock_benchmark": stock, "harness_note": harness_note,
     }
 
 
