@@ -35,6 +35,8 @@ def parse_args():
     ap.add_argument("--ctas", default="16,32,64,128")
     ap.add_argument("--graph", action="store_true", help="replay each batch from a CUDA graph")
     ap.add_argument("--buffers", default="symmetric", choices=["symmetric", "plain"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "nccl"],
+                    help="nccl: time torch.distributed's NCCL collectives on the same sizes (comparator)")
     return ap.parse_args()
 
 
@@ -61,19 +63,52 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    class NcclComm:
+        """torch.distributed NCCL behind the small interface the loop below uses."""
+        nvls = True
+
+        def empty(self, n, dt):
+            return torch.empty(n, dtype=dt, device=dev)
+
+        def all_reduce(self, y, x, op="sum"):
+            dist.all_reduce(x, op={"sum": dist.ReduceOp.SUM, "avg": dist.ReduceOp.AVG, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}[op])
+
+        def reduce_scatter(self, y, x, op="sum"):
+            dist.reduce_scatter_tensor(y, x, op=dist.ReduceOp.SUM if op == "sum" else dist.ReduceOp.AVG)
+
+        def all_gather(self, y, x):
+            dist.all_gather_into_tensor(y, x)
+
+        def check_async_error(self):
+            pass
+
+        def last_call(self):
+            return {"algo": "nccl", "grid": 0}
+
+        def close(self):
+            pass
+
     rows = []
-    for algo in args.algos.split(","):
-        for ctas in [int(c) for c in args.ctas.split(",")]:
-            os.environ["B200CCL_MAX_CTAS"] = str(ctas)
-            port = [0]
-            if rank == 0:
-                s = socket.socket(); s.bind(("127.0.0.1", 0)); port[0] = s.getsockname()[1]; s.close()
-            if world > 1:
-                dist.broadcast_object_list(port, src=0)
-            comm = nn.Communicator(devices=[local], rank=rank, world_size=world, port=port[0], algo=algo)
-            if algo == "nvls" and not comm.nvls:
-                comm.close()
-                continue
+    algos = ["nccl"] if args.impl == "nccl" else args.algos.split(",")
+    cta_list = [0] if args.impl == "nccl" else [int(c) for c in args.ctas.split(",")]
+    for algo in algos:
+        for ctas in cta_list:
+            if args.impl == "nccl":
+                comm = NcclComm()
+                yield_comm = True
+            else:
+                yield_comm = False
+            if not yield_comm:
+                os.environ["B200CCL_MAX_CTAS"] = str(ctas)
+                port = [0]
+                if rank == 0:
+                    s = socket.socket(); s.bind(("127.0.0.1", 0)); port[0] = s.getsockname()[1]; s.close()
+                if world > 1:
+                    dist.broadcast_object_list(port, src=0)
+                comm = nn.Communicator(devices=[local], rank=rank, world_size=world, port=port[0], algo=algo)
+                if algo == "nvls" and not comm.nvls:
+                    comm.close()
+                    continue
             size = args.min_bytes
             while size <= args.max_bytes:
                 if algo == "oneshot" and size > (8 << 20):

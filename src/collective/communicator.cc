@@ -66,6 +66,7 @@ private:
         cudaEvent_t done = nullptr;
         bool launched = false;
         cudaStream_t last_stream = nullptr;
+        bool last_in_capture = false;  // the completion event was last recorded inside a stream capture
     };
 
     void resolve_transport(const CommunicatorConfig& config);
@@ -240,7 +241,7 @@ Communicator::Impl::~Impl() {
     // Work in flight is waited for (destroying a communicator with unsynchronised streams is
     // allowed, as in tests/public_api.cu:904-916 of the reference).
     for (auto& l : local_) {
-        if (l.launched && l.done) {
+        if (l.launched && l.done && !l.last_in_capture) {
             const cudaError_t st = cudaEventSynchronize(l.done);
             if (st != cudaSuccess) {
                 (void)cudaGetLastError();
@@ -323,13 +324,23 @@ void Communicator::Impl::free_symmetric(const std::vector<void*>& ptrs) {
 // (which also keeps a stream capture free of dependencies on events recorded outside it); on a
 // different stream the new launch waits for the previous one's completion event.
 void Communicator::Impl::wait_previous(Local& l, cudaStream_t stream) {
-    if (l.launched && l.last_stream != stream) B2_CUDA(cudaStreamWaitEvent(stream, l.done, 0));
+    if (!l.launched || l.last_stream == stream) return;
+    // An event recorded outside a capture cannot be waited for inside one, and the other way
+    // round; across that boundary the caller's own ordering (capture begin/end, graph launch) holds.
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    B2_CUDA(cudaStreamIsCapturing(stream, &st));
+    const bool capturing = st == cudaStreamCaptureStatusActive;
+    if (capturing != l.last_in_capture) return;
+    B2_CUDA(cudaStreamWaitEvent(stream, l.done, 0));
 }
 
 void Communicator::Impl::record_done(Local& l, cudaStream_t stream) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    B2_CUDA(cudaStreamIsCapturing(stream, &st));
     B2_CUDA(cudaEventRecord(l.done, stream));
     l.launched = true;
     l.last_stream = stream;
+    l.last_in_capture = st == cudaStreamCaptureStatusActive;
 }
 
 void Communicator::Impl::fill_common(dev::CollArgs& a, const Local& l) const {
@@ -460,7 +471,17 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
     shape.output_multicast = out_sym && heap_[out_loc[0].region]->multicast_ptr() != nullptr;
     shape.ring_only = resolved_ != TransportKind::P2p;  // shm, socket, rdma: only the ring crosses those edges
     shape.max_ctas = tuning_.max_ctas;
-    const sched::Plan plan = sched::make_plan(shape, forced_algo_, tuning_);
+    shape.staging_multicast = alloc_ && alloc_->multicast_supported() && (!stage_ || stage_->multicast_ptr() != nullptr);
+    sched::Plan plan = sched::make_plan(shape, forced_algo_, tuning_);
+    if (plan.error.empty() && plan.algo == Algo::Nvls && (plan.stage_in || plan.stage_out)) {
+        // The staging arena is allocated on first use; every rank learns together (the binding is
+        // agreed between processes) whether it got a multicast alias. Without one, plan again.
+        ensure_staging();
+        if (stage_->multicast_ptr() == nullptr) {
+            shape.staging_multicast = false;
+            plan = sched::make_plan(shape, forced_algo_, tuning_);
+        }
+    }
     if (!plan.error.empty()) throw std::invalid_argument(std::string(collective_name(collective)) + ": " + plan.error);
 
     last_ = CallInfo{};
@@ -554,8 +575,10 @@ void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sch
             if (plan.stage_in) a.user_in = static_cast<const char*>(args.send_buffers[i]) + off;
             if (plan.stage_out) a.user_out = static_cast<char*>(args.recv_buffers[i]) + off;
             if (nvls) {
-                a.mc_in = static_cast<const char*>(heap_[in_loc[i].region]->multicast_ptr()) + in_loc[i].offset + off;
-                a.mc_out = static_cast<char*>(heap_[out_loc[i].region]->multicast_ptr()) + out_loc[i].offset + off;
+                a.mc_in = plan.stage_in ? static_cast<const char*>(stage_->multicast_ptr())
+                                        : static_cast<const char*>(heap_[in_loc[i].region]->multicast_ptr()) + in_loc[i].offset + off;
+                a.mc_out = plan.stage_out ? static_cast<char*>(stage_->multicast_ptr()) + staging_half_
+                                          : static_cast<char*>(heap_[out_loc[i].region]->multicast_ptr()) + out_loc[i].offset + off;
             }
         }
         launch_reduce_ranks(args, per, wide, nvls, plan.grid);

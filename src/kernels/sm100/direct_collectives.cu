@@ -32,6 +32,20 @@ __device__ __forceinline__ const A& select_args(const A& one) { return one; }
 template <typename A>
 __device__ __forceinline__ const A& select_args(const LoopPack<A>& all) { return all.r[blockIdx.y]; }
 
+// Copies the packs first, first+stripe, ... below len, four loads in flight per thread.
+template <typename P>
+__device__ __forceinline__ void copy_stripes(void* dst, u64 dst0, const void* src, u64 src0, u64 first, u64 len, u64 stripe) {
+    for (u64 j = first; j < len; j += stripe * 4) {
+        typename P::Raw v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (j + (u64)u * stripe < len) v[u] = P::load(src, src0 + j + (u64)u * stripe);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (j + (u64)u * stripe < len) P::store(dst, dst0 + j + (u64)u * stripe, v[u]);
+    }
+}
+
 template <int N>
 struct UnrollFor {
     static constexpr int value = N == 0 ? 1 : (N >= 8 ? 1 : (N >= 4 ? 2 : (N >= 2 ? 4 : 8)));
@@ -75,7 +89,7 @@ reduce_kernel(const __grid_constant__ ParamT param) {
         for (int s = 0; s < nshards; ++s) {
             const u64 lo = shard_lo(s), len = shard_len(s);
             const u64 dst0 = lo + (u64)s * a.in_stride, src0 = lo + (u64)s * a.uin_stride;
-            for (u64 j = first; j < len; j += stripe) P::store(stage, dst0 + j, P::load(a.user_in, src0 + j));
+            copy_stripes<P>(stage, dst0, a.user_in, src0, first, len, stripe);
         }
     }
 
@@ -175,7 +189,7 @@ reduce_kernel(const __grid_constant__ ParamT param) {
     if (a.user_out != nullptr) {
         for (int s = 0; s < nshards; ++s) {
             const u64 lo = shard_lo(s), len = shard_len(s);
-            for (u64 j = first; j < len; j += stripe) P::store(a.user_out, lo + j, P::load(a.out[rank], lo + j));
+            copy_stripes<P>(a.user_out, lo, a.out[rank], lo, first, len, stripe);
         }
     }
     if (threadIdx.x == 0) own->epoch[blockIdx.x] = epoch;

@@ -7,15 +7,25 @@
 namespace b200ccl::sched {
 
 Tuning default_tuning() {
+    // Measured on 8x B200 (NVSwitch), float sum, symmetric buffers, CUDA-event timing:
+    //  * 8 ranks: the multimem kernel is fastest at every size from 1 KiB (12.6 us) to 1 GiB
+    //    (822 GB/s bus bandwidth); 64 CTAs beat 128 from 32 MiB up.
+    //  * peer kernels, 8 ranks: one-shot 14.7 us up to 8 KiB, two-shot ~16 us up to 64 KiB and faster
+    //    than one-shot from 16 KiB up; two-shot likes 128 CTAs at >= 32 MiB (213 vs 234 us at 64 MiB).
+    //  * 2 ranks: one-shot wins up to 1 MiB (15.7 us), two-shot above; multimem is slower than peer
+    //    access (366 vs 540 GB/s at 64 MiB) and is not used.
     Tuning t{};
-    // One-shot moves (n-1)·S per rank against two-shot's 2(n-1)/n·S but has no second hop.
-    for (int n = 0; n <= kMaxRanks; ++n) t.oneshot_max_bytes[n] = 256u << 10;
-    t.oneshot_max_bytes[2] = 1u << 20;   // at two ranks both move S; one-shot only stores locally
+    for (int n = 0; n <= kMaxRanks; ++n) t.oneshot_max_bytes[n] = 64u << 10;
+    t.oneshot_max_bytes[2] = 1u << 20;
+    t.oneshot_max_bytes[3] = 256u << 10;
     t.oneshot_max_bytes[4] = 256u << 10;
-    t.oneshot_max_bytes[8] = 128u << 10;
-    t.nvls_min_bytes = 64u << 10;
-    t.max_ctas = 64;
+    t.oneshot_max_bytes[8] = 32u << 10;
+    t.nvls_min_bytes = 0;
+    t.max_ctas = 128;
+    t.nvls_max_ctas = 64;
+    t.twoshot_max_ctas = 128;
     t.bytes_per_cta = 32u << 10;
+    t.oneshot_bytes_per_cta = 8u << 10;
     return t;
 }
 
@@ -26,8 +36,12 @@ Tuning tuning_from_env() {
         for (int n = 0; n <= kMaxRanks; ++n) t.oneshot_max_bytes[n] = v;
     }
     t.nvls_min_bytes = env::get_bytes("B200CCL_NVLS_MIN_BYTES", t.nvls_min_bytes);
-    t.max_ctas = static_cast<int>(env::get_int("B200CCL_MAX_CTAS", t.max_ctas));
+    if (env::get("B200CCL_MAX_CTAS")) {
+        t.max_ctas = static_cast<int>(env::get_int("B200CCL_MAX_CTAS", t.max_ctas));
+        t.nvls_max_ctas = t.twoshot_max_ctas = t.max_ctas;  // an explicit cap applies to every algorithm
+    }
     t.bytes_per_cta = env::get_bytes("B200CCL_BYTES_PER_CTA", t.bytes_per_cta);
+    t.oneshot_bytes_per_cta = env::get_bytes("B200CCL_ONESHOT_BYTES_PER_CTA", t.oneshot_bytes_per_cta);
     return t;
 }
 
@@ -38,8 +52,8 @@ std::size_t message_bytes(const CallShape& s) {
 
 namespace {
 
-int grid_for(std::size_t bytes_this_rank_handles, const Tuning& t, int cap) {
-    const std::size_t per = std::max<std::size_t>(t.bytes_per_cta, 1);
+int grid_for(std::size_t bytes_this_rank_handles, const Tuning& t, int cap, std::size_t per_cta = 0) {
+    const std::size_t per = std::max<std::size_t>(per_cta ? per_cta : t.bytes_per_cta, 1);
     std::size_t g = (bytes_this_rank_handles + per - 1) / per;
     g = std::max<std::size_t>(g, 1);
     return static_cast<int>(std::min<std::size_t>(g, static_cast<std::size_t>(std::max(cap, 1))));
@@ -49,8 +63,12 @@ bool nvls_usable(const CallShape& s) {
     // At two ranks the switch saves no traffic over direct peer access and measured slower.
     if (!s.wide || s.nranks < 3) return false;
     switch (s.collective) {
-        case Collective::AllReduce:
-            return (s.redop == RedOp::Sum || s.redop == RedOp::Avg) && s.input_multicast && s.output_multicast;
+        case Collective::AllReduce: {
+            // A side that peers cannot address is staged; the staging arena may itself be multicast-bound.
+            const bool in_ok = s.input_multicast || (!s.peers_read_input && s.staging_multicast);
+            const bool out_ok = s.output_multicast || (!s.peers_write_output && s.staging_multicast);
+            return (s.redop == RedOp::Sum || s.redop == RedOp::Avg) && in_ok && out_ok;
+        }
         case Collective::ReduceScatter:
             return (s.redop == RedOp::Sum || s.redop == RedOp::Avg) && s.input_multicast;
         case Collective::AllGather:
@@ -63,7 +81,7 @@ bool nvls_usable(const CallShape& s) {
 
 Plan make_plan(const CallShape& s, Algo forced, const Tuning& t) {
     Plan p;
-    const int cap = std::min(s.max_ctas > 0 ? s.max_ctas : t.max_ctas, t.max_ctas);
+    const int cap = std::max(1, std::min(s.max_ctas > 0 ? s.max_ctas : t.max_ctas, t.max_ctas));
     const std::size_t bytes = message_bytes(s);
     const std::size_t esz = dtype_size(s.dtype);
 
@@ -122,16 +140,19 @@ Plan make_plan(const CallShape& s, Algo forced, const Tuning& t) {
     }
     p.algo = algo;
     if (algo == Algo::Nvls) {
-        p.grid = grid_for(bytes / s.nranks, t, cap);
+        // Buffers that peers cannot address pass through the (multicast-bound) staging arena.
+        p.stage_in = !s.peers_read_input;
+        p.stage_out = !s.peers_write_output;
+        p.grid = grid_for(bytes / s.nranks * (p.stage_in || p.stage_out ? s.nranks : 1), t, std::min(cap, t.nvls_max_ctas));
     } else if (algo == Algo::OneShot) {
         p.stage_in = !s.peers_read_input;
-        p.grid = grid_for(bytes, t, cap);
+        p.grid = grid_for(bytes, t, cap, t.oneshot_bytes_per_cta);
     } else {
         p.stage_in = !s.peers_read_input;
         p.stage_out = !s.peers_write_output;
         // Staging works on (input arena, output arena) pairs: if either side is staged the
         // kernel still reads/writes the other side in place.
-        p.grid = grid_for(bytes / s.nranks * (p.stage_in || p.stage_out ? s.nranks : 1), t, cap);
+        p.grid = grid_for(bytes / s.nranks * (p.stage_in || p.stage_out ? s.nranks : 1), t, std::min(cap, t.twoshot_max_ctas));
     }
     return p;
 }

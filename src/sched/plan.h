@@ -24,6 +24,7 @@ struct CallShape {
     bool peers_write_output = false;  // peers can store into this call's output directly
     bool input_multicast = false;     // input has a multicast alias (NVLS ld_reduce possible)
     bool output_multicast = false;    // output has a multicast alias (NVLS broadcast possible)
+    bool staging_multicast = false;   // the staging arena has a multicast alias (staged NVLS possible)
     bool in_place = false;
     bool ring_only = false;      // transport without all-pairs peer access: ring is the only choice
     int max_ctas = 64;
@@ -43,8 +44,11 @@ struct Plan {
 struct Tuning {
     std::size_t oneshot_max_bytes[kMaxRanks + 1];  // per nranks: AllReduce sizes up to this use one-shot
     std::size_t nvls_min_bytes = 0;                // NVLS from this size up (when available)
-    int max_ctas = 64;
+    int max_ctas = 128;                            // hard cap for every algorithm (B200CCL_MAX_CTAS)
+    int nvls_max_ctas = 64;                        // more CTAs than this slowed the multimem kernels down
+    int twoshot_max_ctas = 128;
     std::size_t bytes_per_cta = 0;                 // work given to one CTA before another is added
+    std::size_t oneshot_bytes_per_cta = 0;         // one-shot reads every peer's copy: spread it thinner
 };
 Tuning default_tuning();
 Tuning tuning_from_env();
