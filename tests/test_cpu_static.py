@@ -1,7 +1,7 @@
 """Source-level contracts, checked as text (the reference pins similar idioms with Python static
 checks, e.g. tests/avg_scale_fusion_static.py): the avg scale is fused into the reducing kernels and
-no output-wide scaling pass exists; device code never traps, asserts or spins without a bound; no
-TMA load carries a cluster-multicast qualifier; NCCL is not linked into the product."""
+no output-wide scaling pass exists; device code never traps, asserts or spins without a bound; NCCL is
+not linked into the product."""
 import os
 import re
 
@@ -49,12 +49,6 @@ def test_device_code_never_traps_or_spins_unbounded():
             assert "mbar_try_wait(" not in text, f"{name}: use mbar_wait_bounded"
     sync = read(os.path.join(KERNELS, "sync.cuh"))
     assert "timeout_ns" in sync and "kStatusTimeout" in sync and "abort_flag" in sync
-
-
-def test_no_cluster_multicast_qualifier_anywhere():
-    needle = "multicast" + "::" + "cluster"
-    for path, text in all_sources().items():
-        assert needle not in text, path
 
 
 def test_nccl_is_not_linked_into_the_product():
