@@ -42,8 +42,9 @@ def parse_args():
     ap.add_argument("--bytes", type=int, default=HEADLINE_BYTES)
     ap.add_argument("--dtype", default="float", choices=["float", "fp16", "bf16"])
     ap.add_argument("--op", default="sum", choices=["sum", "avg", "max", "min"])
-    ap.add_argument("--buffers", default="symmetric", choices=["symmetric", "plain"],
-                    help="symmetric: tensors from Communicator.empty (peer-mapped, NVLS-capable); plain: torch.empty")
+    ap.add_argument("--buffers", default="symmetric", choices=["symmetric", "plain", "registered"],
+                    help="symmetric: tensors from Communicator.empty (peer-mapped, NVLS-capable); plain: torch.empty "
+                         "(staged inside the kernel); registered: torch.empty + Communicator.register (peer-mapped)")
     ap.add_argument("--algo", default="auto")
     ap.add_argument("--sweep", action="store_true", help="also measure 1 KiB..1 GiB and add it under 'sweep'")
     ap.add_argument("--sweep-max", type=int, default=1 << 30)
@@ -138,7 +139,10 @@ class Runner:
     def alloc(self, numel, dtype):
         if self.comm is not None and self.args.buffers == "symmetric":
             return self.comm.empty(numel, dtype)
-        return self.torch.empty(numel, dtype=dtype, device=self.dev)
+        t = self.torch.empty(numel, dtype=dtype, device=self.dev)
+        if self.comm is not None and self.args.buffers == "registered":
+            self.comm.register(t)
+        return t
 
     def all_reduce(self, out, inp, op):
         if self.is_nccl:

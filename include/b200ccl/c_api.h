@@ -71,6 +71,9 @@ int b2_comm_last_call(const b2_comm* comm, int out[6]);
 /* Symmetric heap: `ptrs` receives one pointer per local rank. Collective over all processes. */
 int b2_comm_alloc_symmetric(b2_comm* comm, size_t bytes, void** ptrs);
 int b2_comm_free_symmetric(b2_comm* comm, void* const* ptrs);
+/* Registration of ordinary device buffers (one pointer per local rank, `bytes` each). Collective. */
+int b2_comm_register(b2_comm* comm, void* const* ptrs, size_t bytes);
+int b2_comm_unregister(b2_comm* comm, void* const* ptrs);
 
 /* Planner (pure function, no GPU needed): out = {algo, grid, stage_in, stage_out, gather_mode}.
  * flags bits: 1 wide, 2 peers_read_input, 4 peers_write_output, 8 input_multicast,

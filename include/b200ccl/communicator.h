@@ -93,6 +93,15 @@ public:
     std::vector<void*> alloc_symmetric(std::size_t bytes);
     void free_symmetric(const std::vector<void*>& ptrs);
 
+    // Registration of ordinary device buffers (cudaMalloc memory, e.g. tensors of a framework's
+    // caching allocator). COLLECTIVE: every process passes its own buffer(s) of `bytes` bytes, one per
+    // local rank, in the same call order. Afterwards collectives on these buffers (or on parts of
+    // them at the same offset on every rank) load and store peers' copies directly instead of
+    // going through the staging arena. In a single-process communicator this is a no-op, since
+    // every device buffer is already peer-addressable. Unregister before freeing the memory.
+    void register_buffers(const std::vector<void*>& ptrs, std::size_t bytes);
+    void unregister_buffers(const std::vector<void*>& ptrs);
+
     CallInfo last_call() const noexcept;
     std::string describe() const;  // topology + per-edge transport report, one line per item
 

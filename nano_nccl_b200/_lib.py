@@ -65,6 +65,8 @@ def load():
     lib.b2_comm_last_call.argtypes = [vp, ctypes.POINTER(ci)]
     lib.b2_comm_alloc_symmetric.argtypes = [vp, cs, ctypes.POINTER(vp)]
     lib.b2_comm_free_symmetric.argtypes = [vp, ctypes.POINTER(vp)]
+    lib.b2_comm_register.argtypes = [vp, ctypes.POINTER(vp), cs]
+    lib.b2_comm_unregister.argtypes = [vp, ctypes.POINTER(vp)]
     _LIB = lib
     return lib
 

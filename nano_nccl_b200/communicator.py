@@ -139,6 +139,25 @@ class Communicator:
             outs.append(raw[: numel * esize].view(dtype).view(*shape))
         return outs[0] if self.local_ranks == 1 else outs
 
+    def register(self, tensors):
+        """Registers ordinary CUDA tensor(s) (one per local rank) so that peers address them directly:
+        later collectives on them, or on slices at the same offset on every rank, skip the staging copy.
+        COLLECTIVE: every process calls it with a tensor of the same size, in the same order. Keep the
+        tensors alive until ``unregister``. Tensors from the virtual-memory (expandable segments)
+        allocator cannot be shared this way; use ``empty()`` for those."""
+        if isinstance(tensors, torch.Tensor):
+            tensors = [tensors]
+        if len(tensors) != self.local_ranks:
+            raise ValueError(f"need one tensor per local rank ({self.local_ranks})")
+        ptrs = (ctypes.c_void_p * self.local_ranks)(*[t.data_ptr() for t in tensors])
+        _lib.check(self._lib.b2_comm_register(self._handle, ptrs, tensors[0].numel() * tensors[0].element_size()))
+
+    def unregister(self, tensors):
+        if isinstance(tensors, torch.Tensor):
+            tensors = [tensors]
+        ptrs = (ctypes.c_void_p * self.local_ranks)(*[t.data_ptr() for t in tensors])
+        _lib.check(self._lib.b2_comm_unregister(self._handle, ptrs))
+
     # -- collectives -----------------------------------------------------------------------------
     def _run(self, coll, outs, inps, op, streams, count, in_place=False):
         if isinstance(inps, torch.Tensor):

@@ -170,6 +170,19 @@ int b2_comm_free_symmetric(b2_comm* c, void* const* ptrs) {
     });
 }
 
+int b2_comm_register(b2_comm* c, void* const* ptrs, size_t bytes) {
+    return guarded([&] {
+        std::vector<void*> v(ptrs, ptrs + c->comm->local_rank_count());
+        c->comm->register_buffers(v, bytes);
+    });
+}
+int b2_comm_unregister(b2_comm* c, void* const* ptrs) {
+    return guarded([&] {
+        std::vector<void*> v(ptrs, ptrs + c->comm->local_rank_count());
+        c->comm->unregister_buffers(v);
+    });
+}
+
 int b2_make_plan(int collective, int dtype, int redop, int nranks, size_t count, unsigned flags, int forced_algo,
                  int out[5]) {
     return guarded([&] {

@@ -19,6 +19,7 @@
 #include "core/env.h"
 #include "kernels/sm100/dev_types.h"
 #include "kernels/sm100/direct_collectives.h"
+#include "mem/ipc_window.h"
 #include "mem/symmetric.h"
 #include "sched/plan.h"
 #include "topo/topology.h"
@@ -35,7 +36,7 @@ namespace {
 bool aligned16(const void* p) { return (reinterpret_cast<std::uintptr_t>(p) & 15u) == 0; }
 
 struct Located {
-    int region = -1;  // index into heap_, or -1
+    int region = -1;  // index into windows_, or -1
     std::size_t offset = 0;
 };
 
@@ -55,6 +56,9 @@ public:
     bool nvls_available() const noexcept { return alloc_ && alloc_->multicast_supported(); }
     std::vector<void*> alloc_symmetric(std::size_t bytes);
     void free_symmetric(const std::vector<void*>& ptrs);
+    void register_buffers(const std::vector<void*>& ptrs, std::size_t bytes);
+    void unregister_buffers(const std::vector<void*>& ptrs);
+    void release_window(const std::vector<void*>& ptrs, const char* what);
     CallInfo last_call() const noexcept { return last_; }
     std::string describe() const;
 
@@ -105,7 +109,17 @@ private:
     std::unique_ptr<mem::SymmetricAllocator> alloc_;
     std::unique_ptr<mem::SymmetricRegion> ctrl_;
     std::unique_ptr<mem::SymmetricRegion> stage_;
-    std::vector<std::unique_ptr<mem::SymmetricRegion>> heap_;
+    // A window is a buffer that exists on every rank and that every rank can address: a symmetric
+    // allocation (with a multicast alias where available) or a registered ordinary buffer.
+    struct Window {
+        std::size_t bytes = 0;  // 0 = released
+        std::vector<void*> ptr;  // per global rank
+        void* mc = nullptr;
+        std::unique_ptr<mem::SymmetricRegion> region;
+        std::unique_ptr<mem::IpcWindow> ipc;
+    };
+    std::vector<Window> windows_;
+    mem::GroupDesc group_;
     std::unique_ptr<RingEngine> ring_;
     CallInfo last_;
     mutable std::string latched_;
@@ -183,6 +197,7 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
         group.want_multicast = config.enable_nvls && resolved_ == TransportKind::P2p;
         group.loopback = loopback_;
         for (const auto& l : local_) group.local.push_back({l.grank, l.device});
+        group_ = group;
         alloc_.reset(new mem::SymmetricAllocator(group));
         ctrl_ = alloc_->allocate(sizeof(dev::ControlBlock), "control");
     }
@@ -250,7 +265,7 @@ Communicator::Impl::~Impl() {
         }
     }
     ring_.reset();
-    heap_.clear();
+    windows_.clear();
     stage_.reset();
     ctrl_.reset();
     for (auto& l : local_) {
@@ -288,10 +303,12 @@ void Communicator::Impl::ensure_staging() {
 }
 
 Located Communicator::Impl::locate(const void* p, std::size_t bytes, int grank) const {
-    for (std::size_t i = 0; i < heap_.size(); ++i) {
-        if (heap_[i] && heap_[i]->contains(grank, p, bytes))
-            return {static_cast<int>(i),
-                    static_cast<std::size_t>(static_cast<const char*>(p) - static_cast<const char*>(heap_[i]->rank_ptr(grank)))};
+    const char* q = static_cast<const char*>(p);
+    for (std::size_t i = 0; i < windows_.size(); ++i) {
+        const Window& w = windows_[i];
+        if (w.bytes == 0) continue;
+        const char* b = static_cast<const char*>(w.ptr[grank]);
+        if (q >= b && q + bytes <= b + w.bytes) return {static_cast<int>(i), static_cast<std::size_t>(q - b)};
     }
     return {};
 }
@@ -299,30 +316,53 @@ Located Communicator::Impl::locate(const void* p, std::size_t bytes, int grank) 
 std::vector<void*> Communicator::Impl::alloc_symmetric(std::size_t bytes) {
     check_async_error();
     if (!alloc_) throw std::runtime_error("symmetric memory is not available with transport shm");
-    auto region = alloc_->allocate(bytes, "user");
+    Window w;
+    w.region = alloc_->allocate(bytes, "user");
+    w.bytes = w.region->bytes();
+    w.mc = w.region->multicast_ptr();
+    for (int g = 0; g < nranks_; ++g) w.ptr.push_back(w.region->rank_ptr(g));
     std::vector<void*> out;
-    for (const auto& l : local_) out.push_back(region->rank_ptr(l.grank));
-    heap_.push_back(std::move(region));
+    for (const auto& l : local_) out.push_back(w.ptr[l.grank]);
+    windows_.push_back(std::move(w));
     return out;
 }
 
-void Communicator::Impl::free_symmetric(const std::vector<void*>& ptrs) {
+void Communicator::Impl::release_window(const std::vector<void*>& ptrs, const char* what) {
     if (ptrs.empty()) return;
-    for (auto& r : heap_) {
-        if (r && r->rank_ptr(local_[0].grank) == ptrs[0]) {
+    for (auto& w : windows_) {
+        if (w.bytes != 0 && w.ptr[local_[0].grank] == ptrs[0]) {
             for (auto& l : local_)
-                if (l.launched) B2_CUDA(cudaEventSynchronize(l.done));
+                if (l.launched && !l.last_in_capture) B2_CUDA(cudaEventSynchronize(l.done));
             if (bootstrap_) bootstrap_->barrier();  // no peer may still be using it
-            r.reset();
+            w.bytes = 0;
+            w.region.reset();
+            w.ipc.reset();
             return;
         }
     }
-    throw std::invalid_argument("free_symmetric: pointer was not returned by alloc_symmetric");
+    throw std::invalid_argument(std::string(what) + ": pointer does not name a live window of this communicator");
 }
 
-// Successive collectives of one rank run in issue order. On the same stream that is stream order
-// (which also keeps a stream capture free of dependencies on events recorded outside it); on a
-// different stream the new launch waits for the previous one's completion event.
+void Communicator::Impl::free_symmetric(const std::vector<void*>& ptrs) { release_window(ptrs, "free_symmetric"); }
+
+void Communicator::Impl::register_buffers(const std::vector<void*>& ptrs, std::size_t bytes) {
+    check_async_error();
+    if (ptrs.size() != local_.size()) throw std::invalid_argument("register_buffers: one pointer per local rank");
+    if (bytes == 0) throw std::invalid_argument("register_buffers: size must be positive");
+    if (!multiprocess_) return;  // one process: every device buffer is already peer-addressable
+    if (resolved_ == TransportKind::Shm) throw std::runtime_error("register_buffers: not available with transport shm");
+    Window w;
+    w.ipc = mem::IpcWindow::create(group_, ptrs, bytes);
+    w.bytes = bytes;
+    for (int g = 0; g < nranks_; ++g) w.ptr.push_back(w.ipc->rank_ptr(g));
+    windows_.push_back(std::move(w));
+}
+
+void Communicator::Impl::unregister_buffers(const std::vector<void*>& ptrs) {
+    if (!multiprocess_) return;
+    release_window(ptrs, "unregister_buffers");
+}
+
 void Communicator::Impl::wait_previous(Local& l, cudaStream_t stream) {
     if (!l.launched || l.last_stream == stream) return;
     // An event recorded outside a capture cannot be waited for inside one, and the other way
@@ -467,8 +507,8 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
     shape.in_place = in_place;
     shape.peers_read_input = direct_peer_pointers() || in_sym;
     shape.peers_write_output = direct_peer_pointers() || out_sym;
-    shape.input_multicast = in_sym && heap_[in_loc[0].region]->multicast_ptr() != nullptr;
-    shape.output_multicast = out_sym && heap_[out_loc[0].region]->multicast_ptr() != nullptr;
+    shape.input_multicast = in_sym && windows_[in_loc[0].region].mc != nullptr;
+    shape.output_multicast = out_sym && windows_[out_loc[0].region].mc != nullptr;
     shape.ring_only = resolved_ != TransportKind::P2p;  // shm, socket, rdma: only the ring crosses those edges
     shape.max_ctas = tuning_.max_ctas;
     shape.staging_multicast = alloc_ && alloc_->multicast_supported() && (!stage_ || stage_->multicast_ptr() != nullptr);
@@ -562,13 +602,13 @@ void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sch
                 // input table
                 if (plan.stage_in) a.in[p] = stage_->rank_ptr(p);
                 else if (in_loc[i].region >= 0)
-                    a.in[p] = static_cast<const char*>(heap_[in_loc[i].region]->rank_ptr(p)) + in_loc[i].offset + off;
+                    a.in[p] = static_cast<const char*>(windows_[in_loc[i].region].ptr[p]) + in_loc[i].offset + off;
                 else if (direct) a.in[p] = static_cast<const char*>(args.send_buffers[p]) + off;
                 // output table
                 if (plan.stage_out) a.out[p] = static_cast<char*>(stage_->rank_ptr(p)) + staging_half_;
                 else if (oneshot) a.out[p] = nullptr;
                 else if (out_loc[i].region >= 0)
-                    a.out[p] = static_cast<char*>(heap_[out_loc[i].region]->rank_ptr(p)) + out_loc[i].offset + off;
+                    a.out[p] = static_cast<char*>(windows_[out_loc[i].region].ptr[p]) + out_loc[i].offset + off;
                 else if (direct) a.out[p] = static_cast<char*>(args.recv_buffers[p]) + off;
             }
             if (oneshot) a.out[local_[i].grank] = static_cast<char*>(args.recv_buffers[i]) + off;
@@ -576,9 +616,9 @@ void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sch
             if (plan.stage_out) a.user_out = static_cast<char*>(args.recv_buffers[i]) + off;
             if (nvls) {
                 a.mc_in = plan.stage_in ? static_cast<const char*>(stage_->multicast_ptr())
-                                        : static_cast<const char*>(heap_[in_loc[i].region]->multicast_ptr()) + in_loc[i].offset + off;
+                                        : static_cast<const char*>(windows_[in_loc[i].region].mc) + in_loc[i].offset + off;
                 a.mc_out = plan.stage_out ? static_cast<char*>(stage_->multicast_ptr()) + staging_half_
-                                          : static_cast<char*>(heap_[out_loc[i].region]->multicast_ptr()) + out_loc[i].offset + off;
+                                          : static_cast<char*>(windows_[out_loc[i].region].mc) + out_loc[i].offset + off;
             }
         }
         launch_reduce_ranks(args, per, wide, nvls, plan.grid);
@@ -610,12 +650,12 @@ void Communicator::Impl::launch_reduce_scatter(const CollectiveArgs& args, const
             for (int p = 0; p < nranks_; ++p) {
                 if (plan.stage_in) a.in[p] = stage_->rank_ptr(p);
                 else if (in_loc[i].region >= 0)
-                    a.in[p] = static_cast<const char*>(heap_[in_loc[i].region]->rank_ptr(p)) + in_loc[i].offset + off;
+                    a.in[p] = static_cast<const char*>(windows_[in_loc[i].region].ptr[p]) + in_loc[i].offset + off;
                 else if (direct) a.in[p] = static_cast<const char*>(args.send_buffers[p]) + off;
             }
             a.out[local_[i].grank] = static_cast<char*>(args.recv_buffers[i]) + off;
             if (plan.stage_in) a.user_in = static_cast<const char*>(args.send_buffers[i]) + off;
-            if (nvls) a.mc_in = static_cast<const char*>(heap_[in_loc[i].region]->multicast_ptr()) + in_loc[i].offset + off;
+            if (nvls) a.mc_in = static_cast<const char*>(windows_[in_loc[i].region].mc) + in_loc[i].offset + off;
         }
         launch_reduce_ranks(args, per, wide, nvls, plan.grid);
     }
@@ -656,11 +696,11 @@ void Communicator::Impl::launch_all_gather(const CollectiveArgs& args, const sch
                 if (plan.gather_mode == 1) {  // pull: need everyone's input
                     if (plan.stage_in) a.in[p] = stage_->rank_ptr(p);
                     else if (in_loc[i].region >= 0)
-                        a.in[p] = static_cast<const char*>(heap_[in_loc[i].region]->rank_ptr(p)) + in_loc[i].offset + off;
+                        a.in[p] = static_cast<const char*>(windows_[in_loc[i].region].ptr[p]) + in_loc[i].offset + off;
                     else if (direct) a.in[p] = static_cast<const char*>(args.send_buffers[p]) + off;
                 } else if (plan.gather_mode == 0) {  // push: need everyone's output
                     if (out_loc[i].region >= 0)
-                        a.out[p] = static_cast<char*>(heap_[out_loc[i].region]->rank_ptr(p)) + out_loc[i].offset + off;
+                        a.out[p] = static_cast<char*>(windows_[out_loc[i].region].ptr[p]) + out_loc[i].offset + off;
                     else if (direct) a.out[p] = static_cast<char*>(args.recv_buffers[p]) + off;
                 }
             }
@@ -668,7 +708,7 @@ void Communicator::Impl::launch_all_gather(const CollectiveArgs& args, const sch
             if (plan.gather_mode != 0) a.out[local_[i].grank] = static_cast<char*>(args.recv_buffers[i]) + off;
             if (plan.stage_in) a.user_in = static_cast<const char*>(args.send_buffers[i]) + off;
             if (plan.gather_mode == 2)
-                a.mc_out = static_cast<char*>(heap_[out_loc[i].region]->multicast_ptr()) + out_loc[i].offset + off;
+                a.mc_out = static_cast<char*>(windows_[out_loc[i].region].mc) + out_loc[i].offset + off;
         }
         launch_gather_ranks(args, per, plan.grid);
     }
@@ -710,6 +750,8 @@ int Communicator::first_global_rank() const noexcept { return impl_->first_globa
 TransportKind Communicator::transport() const noexcept { return impl_->transport(); }
 bool Communicator::nvls_available() const noexcept { return impl_->nvls_available(); }
 std::vector<void*> Communicator::alloc_symmetric(std::size_t bytes) { return impl_->alloc_symmetric(bytes); }
+void Communicator::register_buffers(const std::vector<void*>& ptrs, std::size_t bytes) { impl_->register_buffers(ptrs, bytes); }
+void Communicator::unregister_buffers(const std::vector<void*>& ptrs) { impl_->unregister_buffers(ptrs); }
 void Communicator::free_symmetric(const std::vector<void*>& ptrs) { impl_->free_symmetric(ptrs); }
 CallInfo Communicator::last_call() const noexcept { return impl_->last_call(); }
 std::string Communicator::describe() const { return impl_->describe(); }

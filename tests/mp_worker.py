@@ -57,6 +57,18 @@ def main():
                     comm.all_reduce(sx, op="sum")  # in place
                     torch.cuda.synchronize()
                     assert (sx.float() - ref).abs().max().item() <= tol[dtype] * 2
+                    # ordinary tensors, registered: peers read and write them directly
+                    rx, ro = x.clone(), torch.empty_like(x)
+                    comm.register(rx)
+                    comm.register(ro)
+                    comm.all_reduce(ro, rx, op="sum")
+                    torch.cuda.synchronize()
+                    comm.check_async_error()
+                    info = comm.last_call()
+                    assert not info["staged_in"] and not info["staged_out"], info
+                    assert (ro.float() - ref).abs().max().item() <= tol[dtype] * 2
+                    comm.unregister(rx)
+                    comm.unregister(ro)
                 if numel % world == 0:
                     blk = numel // world
                     rs = torch.empty(blk, device="cuda", dtype=dtype)
