@@ -38,7 +38,7 @@ ProxyBase::~ProxyBase() {
 void ProxyBase::start() {
     if (!thread_.joinable()) thread_ = std::thread([this] { run(); });
 }
-void ProxyBase::stop() noexcept { stop_requested_ = true; }
+void ProxyBase::stop() noexcept { stop_requested_.store(true, std::memory_order_release); }
 void ProxyBase::shutdown() noexcept { connection_.shutdown_both(); }
 void ProxyBase::join() noexcept {
     if (thread_.joinable()) thread_.join();

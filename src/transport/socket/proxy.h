@@ -59,7 +59,7 @@ protected:
     ProxyIdentity identity_;
     int numa_node_;
     std::shared_ptr<AsyncErrorState> errors_;
-    volatile bool stop_requested_ = false;
+    std::atomic<bool> stop_requested_{false};
     std::thread thread_;
     std::atomic<std::uint64_t> step_{0};
     std::atomic<std::uint64_t> slices_{0};

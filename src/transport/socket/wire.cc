@@ -48,9 +48,9 @@ void recv_all(int fd, void* data, std::size_t bytes) {
     }
 }
 
-bool wait_readable(int fd, const volatile bool* stop) {
+bool wait_readable(int fd, const std::atomic<bool>* stop) {
     for (;;) {
-        if (stop && *stop) return false;
+        if (stop && stop->load(std::memory_order_acquire)) return false;
         pollfd pfd{fd, POLLIN, 0};
         const int pr = ::poll(&pfd, 1, 20);
         if (pr > 0) return true;

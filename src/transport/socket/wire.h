@@ -6,6 +6,7 @@
 // capacity is rejected before any payload byte is copied (socket_proxy.cc:150-170); TCP_NODELAY.
 #pragma once
 
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 
@@ -36,7 +37,7 @@ void set_tcp_nodelay(int fd);  // ignored on non-TCP sockets (tests use AF_UNIX 
 void send_all(int fd, const void* data, std::size_t bytes);
 void recv_all(int fd, void* data, std::size_t bytes);
 // Waits until `fd` is readable or `*stop` becomes true; returns false when stopped.
-bool wait_readable(int fd, const volatile bool* stop);
+bool wait_readable(int fd, const std::atomic<bool>* stop);
 
 void send_slice(int fd, const void* payload, std::uint32_t payload_bytes);
 // Reads the header, rejects payload_bytes > capacity (throws, nothing copied), then the payload.
