@@ -24,6 +24,12 @@ def test_bench_cli_verifies(native_build, args):
     assert len(rows) == 3 and all(r[9] == "0" for r in rows), proc.stdout
 
 
+def test_public_api_program(native_build):
+    proc = run_native("test_public_api", env={"B200CCL_WAIT_TIMEOUT_MS": "3000"})
+    assert proc.returncode == 0, proc.stdout + proc.stderr
+    assert "public api ok" in proc.stdout
+
+
 def test_smoke_entry():
     import __graft_entry__ as entry
     entry.smoke()
