@@ -398,6 +398,7 @@ void Communicator::Impl::launch_reduce_ranks(const CollectiveArgs& args, std::ve
     kernels::LaunchConfig cfg;
     cfg.grid = std::min(grid, dev::kMaxCtas);
     cfg.block = dev::kBlockThreads;
+    cfg.nvls_unroll = tuning_.nvls_unroll;
     try {
         if (loopback_) {
             DeviceGuard guard(local_[0].device);

@@ -60,12 +60,13 @@ reduce_kernel(const __grid_constant__ ParamT param) {
     using Raw = typename P::Raw;
     constexpr int kElems = P::kElems;
     constexpr int NN = N > 0 ? N : kMaxRanks;
-    constexpr int kU = kNvls ? 4 : UnrollFor<N>::value;
+    // For the multimem variant the N slot carries the unroll factor (the rank count is a run-time value there).
+    constexpr int kU = kNvls ? (N > 0 ? N : 4) : UnrollFor<N>::value;
 
     __shared__ u64 s_epoch;
     const CollArgs& a = select_args(param);
 
-    const int n = N > 0 ? N : a.nranks;
+    const int n = (N > 0 && !kNvls) ? N : a.nranks;
     const int rank = a.rank;
     ControlBlock* own = a.ctrl[rank];
     if (threadIdx.x == 0) s_epoch = own->epoch[blockIdx.x];
@@ -286,7 +287,9 @@ cudaError_t launch(void (*kernel)(ParamT), const ParamT& param, const LaunchConf
 template <typename T, typename Op, template <class> class PackT, bool kNvls, typename ParamT>
 cudaError_t launch_reduce_n(int nranks, const ParamT& param, const LaunchConfig& cfg) {
     if constexpr (kNvls) {
-        return launch(reduce_kernel<T, Op, 0, PackT, true, ParamT>, param, cfg);
+        if (cfg.nvls_unroll >= 8) return launch(reduce_kernel<T, Op, 8, PackT, true, ParamT>, param, cfg);
+        if (cfg.nvls_unroll <= 2) return launch(reduce_kernel<T, Op, 2, PackT, true, ParamT>, param, cfg);
+        return launch(reduce_kernel<T, Op, 4, PackT, true, ParamT>, param, cfg);
     } else if constexpr (PackT<T>::kBytes != 16) {
         return launch(reduce_kernel<T, Op, 0, PackT, false, ParamT>, param, cfg);
     } else {

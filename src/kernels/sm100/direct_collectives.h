@@ -15,6 +15,7 @@ struct LaunchConfig {
     // Loopback emulation: one cooperative launch plays `loop_ranks` ranks (blockIdx.y = rank)
     // and `args` points to that many argument structs. 0 → normal launch of args[0].
     int loop_ranks = 0;
+    int nvls_unroll = 4;  // multimem loads in flight per thread (2, 4 or 8)
 };
 
 // wide: 16-byte packs (all pointers 16-byte aligned, lengths in 16-byte units); else one element

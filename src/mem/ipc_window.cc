@@ -4,7 +4,10 @@
 #include "mem/cu_driver.h"
 
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <stdexcept>
+#include <string>
 
 namespace b200ccl::mem {
 
@@ -31,6 +34,43 @@ void* allocation_base(void* p) {
     size_t size = 0;
     cu::check(reinterpret_cast<Fn>(fn)(&base, &size, reinterpret_cast<CUdeviceptr>(p)), "cuMemGetAddressRange");
     return reinterpret_cast<void*>(base);
+}
+
+// An allocation may hold several registered buffers (framework allocators carve tensors out of
+// large segments). Each exported allocation is mapped once per process and reference-counted.
+struct Mapping {
+    void* base = nullptr;
+    int refs = 0;
+};
+std::mutex g_map_mutex;
+std::map<std::string, Mapping> g_mappings;  // key: raw bytes of the IPC handle
+
+void* open_shared(const cudaIpcMemHandle_t& h) {
+    const std::string key(reinterpret_cast<const char*>(&h), sizeof(h));
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    Mapping& m = g_mappings[key];
+    if (m.refs == 0) {
+        const cudaError_t st = cudaIpcOpenMemHandle(&m.base, h, cudaIpcMemLazyEnablePeerAccess);
+        if (st != cudaSuccess) {
+            g_mappings.erase(key);
+            throw_cuda(st, "cudaIpcOpenMemHandle", __FILE__, __LINE__);
+        }
+    }
+    ++m.refs;
+    return m.base;
+}
+
+void close_shared(void* base) {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    for (auto it = g_mappings.begin(); it != g_mappings.end(); ++it) {
+        if (it->second.base == base) {
+            if (--it->second.refs == 0) {
+                cudaIpcCloseMemHandle(base);
+                g_mappings.erase(it);
+            }
+            return;
+        }
+    }
 }
 
 }  // namespace
@@ -73,8 +113,7 @@ std::unique_ptr<IpcWindow> IpcWindow::create(const GroupDesc& group, const std::
                 const Record& r = all[static_cast<std::size_t>(p) * n + g];
                 if (!r.valid) continue;
                 if (r.bytes != bytes) throw std::runtime_error("ranks registered buffers of different sizes");
-                void* base = nullptr;
-                B2_CUDA(cudaIpcOpenMemHandle(&base, r.handle, cudaIpcMemLazyEnablePeerAccess));
+                void* base = open_shared(r.handle);
                 w->opened_.push_back({group.local[0].device, base});
                 w->rank_ptr_[g] = static_cast<char*>(base) + r.offset;
             }
@@ -95,7 +134,7 @@ IpcWindow::~IpcWindow() {
         int prev = 0;
         cudaGetDevice(&prev);
         cudaSetDevice(o.device);
-        cudaIpcCloseMemHandle(o.base);
+        close_shared(o.base);
         cudaSetDevice(prev);
     }
     (void)cudaGetLastError();

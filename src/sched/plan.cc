@@ -40,6 +40,8 @@ Tuning tuning_from_env() {
         t.max_ctas = static_cast<int>(env::get_int("B200CCL_MAX_CTAS", t.max_ctas));
         t.nvls_max_ctas = t.twoshot_max_ctas = t.max_ctas;  // an explicit cap applies to every algorithm
     }
+    t.nvls_max_ctas = static_cast<int>(env::get_int("B200CCL_NVLS_MAX_CTAS", t.nvls_max_ctas));
+    t.nvls_unroll = static_cast<int>(env::get_int("B200CCL_NVLS_UNROLL", t.nvls_unroll));
     t.bytes_per_cta = env::get_bytes("B200CCL_BYTES_PER_CTA", t.bytes_per_cta);
     t.oneshot_bytes_per_cta = env::get_bytes("B200CCL_ONESHOT_BYTES_PER_CTA", t.oneshot_bytes_per_cta);
     return t;

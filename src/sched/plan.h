@@ -47,6 +47,7 @@ struct Tuning {
     int max_ctas = 128;                            // hard cap for every algorithm (B200CCL_MAX_CTAS)
     int nvls_max_ctas = 64;                        // more CTAs than this slowed the multimem kernels down
     int twoshot_max_ctas = 128;
+    int nvls_unroll = 4;                           // multimem loads in flight per thread (B200CCL_NVLS_UNROLL)
     std::size_t bytes_per_cta = 0;                 // work given to one CTA before another is added
     std::size_t oneshot_bytes_per_cta = 0;         // one-shot reads every peer's copy: spread it thinner
 };
