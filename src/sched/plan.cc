@@ -7,20 +7,22 @@
 namespace b200ccl::sched {
 
 Tuning default_tuning() {
-    // Measured on 8x B200 (NVSwitch), float sum, symmetric buffers, CUDA-event timing:
-    //  * 8 ranks: the multimem kernel is fastest at every size from 1 KiB (12.6 us) to 1 GiB
-    //    (822 GB/s bus bandwidth); 64 CTAs beat 128 from 32 MiB up.
-    //  * peer kernels, 8 ranks: one-shot 14.7 us up to 8 KiB, two-shot ~16 us up to 64 KiB and faster
-    //    than one-shot from 16 KiB up; two-shot likes 128 CTAs at >= 32 MiB (213 vs 234 us at 64 MiB).
-    //  * 2 ranks: one-shot wins up to 1 MiB (15.7 us), two-shot above; multimem is slower than peer
-    //    access (366 vs 540 GB/s at 64 MiB) and is not used.
+    // Measured on 8x B200 (NVSwitch), float sum, CUDA-event timing, maximum over ranks
+    // (tables under tuning/):
+    //  * 8 ranks, device time from CUDA-graph replay: one-shot 9.7 us up to 8 KiB; the multimem kernel
+    //    10.6-10.9 us flat up to 64 KiB and fastest from 16 KiB (10.8 vs 11.8 us one-shot) to 1 GiB
+    //    (822 GB/s bus bandwidth); peer two-shot 10.4 us at 16-32 KiB and ahead of one-shot from there.
+    //    64 CTAs beat 128 for multimem from 32 MiB up; two-shot likes 128 CTAs (199 vs 234 us at 64 MiB).
+    //  * 4 ranks: one-shot 8.5 us up to 8 KiB, two-shot 9.3 us at 16-64 KiB, multimem fastest from
+    //    128 KiB (10.3 vs 13.1 us) and level with two-shot at >= 4 MiB (608 vs 601 GB/s at 64 MiB).
+    //  * 2 ranks: one-shot wins up to 1 MiB (15.7 us), two-shot above (585 GB/s at 64 MiB); multimem is
+    //    slower than peer access there (366 GB/s) and is not used.
     Tuning t{};
-    for (int n = 0; n <= kMaxRanks; ++n) t.oneshot_max_bytes[n] = 64u << 10;
+    for (int n = 0; n <= kMaxRanks; ++n) t.oneshot_max_bytes[n] = 8u << 10;
+    t.oneshot_max_bytes[1] = 0;
     t.oneshot_max_bytes[2] = 1u << 20;
-    t.oneshot_max_bytes[3] = 256u << 10;
-    t.oneshot_max_bytes[4] = 256u << 10;
-    t.oneshot_max_bytes[8] = 32u << 10;
-    t.nvls_min_bytes = 0;
+    t.oneshot_max_bytes[3] = 16u << 10;
+    t.nvls_min_bytes = 16u << 10;
     t.max_ctas = 128;
     t.nvls_max_ctas = 64;
     t.twoshot_max_ctas = 128;
