@@ -87,9 +87,6 @@ def busbw(nbytes, seconds, n):
     return alg * 2 * (n - 1) / n if n > 1 else alg
 
 
-TORCH_DTYPES = {}
-
-
 def torch_dtype(name):
     import torch
     return {"float": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[name]

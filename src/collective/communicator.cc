@@ -73,7 +73,7 @@ private:
         bool last_in_capture = false;  // the completion event was last recorded inside a stream capture
     };
 
-    void resolve_transport(const CommunicatorConfig& config);
+    void resolve_transport();
     void ensure_staging();
     Located locate(const void* p, std::size_t bytes, int grank) const;
     void wait_previous(Local& l, cudaStream_t stream);
@@ -186,7 +186,7 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
     }
 
     topo_ = topo::discover(config.devices);
-    resolve_transport(config);
+    resolve_transport();
 
     // Peer-mapped memory exists for every transport except SHM, whose point is to work
     // without peer access (everything it shares lives in mapped host memory).
@@ -209,14 +209,12 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
         std::memset(l.status, 0, sizeof(dev::Status));
         B2_CUDA(cudaEventCreateWithFlags(&l.done, cudaEventDisableTiming));
     }
-    if (resolved_ != TransportKind::P2p || forced_algo_ == Algo::Ring) {
-        // Ring engine is built on first use; nothing to do here.
-    }
+    // (The ring engine, its FIFOs and any network edges are built on the first call that needs them.)
     log_info("communicator: %d ranks (%d local, first %d), transport %s, nvls %s", nranks_, nlocal, first,
              transport_name(resolved_), nvls_available() ? "yes" : "no");
 }
 
-void Communicator::Impl::resolve_transport(const CommunicatorConfig& config) {
+void Communicator::Impl::resolve_transport() {
     std::vector<int> devs;
     for (const auto& l : local_)
         if (std::find(devs.begin(), devs.end(), l.device) == devs.end()) devs.push_back(l.device);
@@ -249,7 +247,6 @@ void Communicator::Impl::resolve_transport(const CommunicatorConfig& config) {
             break;
         default: throw std::invalid_argument("bad transport");
     }
-    (void)config;
 }
 
 Communicator::Impl::~Impl() {
