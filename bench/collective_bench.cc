@@ -1,6 +1,6 @@
 // Command-line benchmark. Flags and table columns follow nano-nccl's
 // nano_nccl_all_reduce_bench (benchmarks/all_reduce_bench.cu:50-58 usage, 395-411 table); added
-// are --collective, --nranks, --loopback, --symmetric, --data and --json. Exit status is
+// are --collective, --nranks, --loopback, --symmetric, --graph, --data and --json. Exit status is
 // non-zero when any row has #wrong != 0, as in the reference (all_reduce_bench.cu:414-419).
 #include "b200ccl/bench.h"
 
@@ -17,7 +17,7 @@ void usage(const char* argv0) {
     std::fprintf(stderr,
                  "Usage: %s [--collective all_reduce|reduce_scatter|all_gather] [--algo auto|oneshot|twoshot|nvls|ring]\n"
                  "          [--dtype float|fp16|bf16] [--redop sum|avg|max|min] [--transport auto|shm|p2p|rdma]\n"
-                 "          [--nranks N] [--loopback] [--symmetric] [--data uniform|normal]\n"
+                 "          [--nranks N] [--loopback] [--symmetric] [--graph] [--data uniform|normal]\n"
                  "          [-b bytes] [-e bytes] [-f factor] [-w warmup] [-n iters] [--json file]\n",
                  argv0);
 }
@@ -52,6 +52,7 @@ int main(int argc, char** argv) {
         else if (a == "--nranks") { const char* v = next(); ok = v; if (v) cfg.nranks = std::atoi(v); }
         else if (a == "--loopback") cfg.loopback = true;
         else if (a == "--symmetric") cfg.symmetric = true;
+        else if (a == "--graph") cfg.graph = true;
         else if (a == "--data") { const char* v = next(); ok = v && (!std::strcmp(v, "uniform") || !std::strcmp(v, "normal")); if (ok) cfg.uniform_data = !std::strcmp(v, "uniform"); }
         else if (a == "-b") { const char* v = next(); ok = v && size_arg(v, &cfg.min_bytes); }
         else if (a == "-e") { const char* v = next(); ok = v && size_arg(v, &cfg.max_bytes); }

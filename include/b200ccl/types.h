@@ -66,6 +66,7 @@ struct BenchConfig {
     bool loopback = false;       // all ranks emulated on device 0 by one launch
     bool symmetric = false;      // buffers taken from the communicator's symmetric heap
     bool uniform_data = true;    // uniform[-1,1) seeded per rank; false → N(0,1)
+    bool graph = false;          // capture the timed batch into CUDA graphs and time their replay
 };
 
 struct BenchResult {

@@ -3,12 +3,15 @@
 
 #include "b200ccl/traits.h"
 #include "collective/bench_profiling.h"
+#include "core/buffers.h"
 #include "core/check.h"
 #include "core/datagen.h"
+#include "core/stream.h"
 
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
+#include <memory>
 
 namespace b200ccl {
 
@@ -106,9 +109,13 @@ namespace {
 
 struct RankState {
     int device = 0;
+    std::unique_ptr<Stream> own_stream;  // null for emulated ranks, which share rank 0's stream
     cudaStream_t stream = nullptr;
+    std::unique_ptr<Event> start_ev, stop_ev;  // timing events on `stream`
     cudaEvent_t start = nullptr, stop = nullptr;
     std::vector<void*> send, recv;  // one per buffer set
+    DeviceBuffer<unsigned long long> wrong_buf;
+    DeviceBuffer<unsigned int> max_abs_buf;
     unsigned long long* wrong = nullptr;
     unsigned int* max_abs = nullptr;
 };
@@ -155,18 +162,21 @@ int run_collective_bench(const BenchConfig& config, std::vector<BenchResult>* re
     std::vector<RankState> ranks(nranks);
     for (int r = 0; r < nranks; ++r) {
         ranks[r].device = config.loopback ? 0 : r;
-        DeviceGuard guard(ranks[r].device);
-        B2_CUDA(cudaStreamCreateWithFlags(&ranks[r].stream, cudaStreamNonBlocking));
-        B2_CUDA(cudaEventCreate(&ranks[r].start));
-        B2_CUDA(cudaEventCreate(&ranks[r].stop));
-        B2_CUDA(cudaMalloc(&ranks[r].wrong, sizeof(unsigned long long)));
-        B2_CUDA(cudaMalloc(&ranks[r].max_abs, sizeof(unsigned int)));
-    }
-    if (config.loopback) {  // one launch plays all ranks: they share rank 0's stream
-        for (int r = 1; r < nranks; ++r) {
-            cudaStreamDestroy(ranks[r].stream);
-            ranks[r].stream = ranks[0].stream;
+        RankState& st = ranks[r];
+        if (!config.loopback || r == 0) {
+            st.own_stream.reset(new Stream(st.device));
+            st.stream = st.own_stream->get();
+        } else {
+            st.stream = ranks[0].stream;  // one launch plays all ranks: they share rank 0's stream
         }
+        st.start_ev.reset(new Event(st.device, /*timing=*/true));
+        st.stop_ev.reset(new Event(st.device, /*timing=*/true));
+        st.start = st.start_ev->get();
+        st.stop = st.stop_ev->get();
+        st.wrong_buf.reset(st.device, 1);
+        st.max_abs_buf.reset(st.device, 1);
+        st.wrong = st.wrong_buf.get();
+        st.max_abs = st.max_abs_buf.get();
     }
     auto sync_all = [&] {
         for (int r = 0; r < nranks; ++r) {
@@ -175,6 +185,7 @@ int run_collective_bench(const BenchConfig& config, std::vector<BenchResult>* re
         }
     };
 
+    PinnedBuffer<unsigned long long> readback(2);
     int rc = 0;
     for (std::size_t bytes : make_sizes(config.min_bytes, config.max_bytes, config.factor)) {
         const std::size_t count = std::max<std::size_t>(bytes / esz, 1);
@@ -236,7 +247,35 @@ int run_collective_bench(const BenchConfig& config, std::vector<BenchResult>* re
                 DeviceGuard guard(ranks[r].device);
                 B2_CUDA(cudaEventRecord(ranks[r].start, ranks[r].stream));
             }
-            {
+            if (config.graph) {
+                // The whole batch is captured once per rank stream and replayed: launch cost leaves the
+                // measurement and what remains is the device time of the collectives.
+                std::vector<GraphExec> graphs;
+                for (int r = 0; r < record_ranks; ++r) {
+                    DeviceGuard guard(ranks[r].device);
+                    B2_CUDA(cudaStreamBeginCapture(ranks[r].stream, cudaStreamCaptureModeRelaxed));
+                }
+                for (int i = 0; i < config.iters; ++i) issue(i % sets);
+                for (int r = 0; r < record_ranks; ++r) {
+                    DeviceGuard guard(ranks[r].device);
+                    cudaGraph_t g = nullptr;
+                    B2_CUDA(cudaStreamEndCapture(ranks[r].stream, &g));
+                    graphs.emplace_back(g);
+                    B2_CUDA(cudaGraphDestroy(g));
+                }
+                for (int pass = 0; pass < 2; ++pass) {  // first replay warms up, second is timed
+                    if (pass == 1)
+                        for (int r = 0; r < record_ranks; ++r) {
+                            DeviceGuard guard(ranks[r].device);
+                            B2_CUDA(cudaEventRecord(ranks[r].start, ranks[r].stream));
+                        }
+                    for (int r = 0; r < record_ranks; ++r) {
+                        DeviceGuard guard(ranks[r].device);
+                        graphs[r].launch(ranks[r].stream);
+                    }
+                    if (pass == 0) sync_all();
+                }
+            } else {
                 // Capture window and ranges cover the measured batch only (no-ops in normal builds).
                 ProfilerSession session;
                 NvtxRange size_range(bench_range_name(collective_name(coll), count * esz));
@@ -266,6 +305,7 @@ int run_collective_bench(const BenchConfig& config, std::vector<BenchResult>* re
                 DeviceGuard guard(ranks[r].device);
                 B2_CUDA(cudaMemsetAsync(ranks[r].wrong, 0, sizeof(unsigned long long), ranks[r].stream));
                 B2_CUDA(cudaMemsetAsync(ranks[r].max_abs, 0, sizeof(unsigned int), ranks[r].stream));
+                readback.get()[0] = readback.get()[1] = 0;
                 if (coll == Collective::AllGather) {
                     for (int src = 0; src < nranks; ++src)
                         bench_verify(static_cast<char*>(ranks[r].recv[last_set]) + src * count * esz, count, config.dtype,
@@ -276,12 +316,13 @@ int run_collective_bench(const BenchConfig& config, std::vector<BenchResult>* re
                     bench_verify(ranks[r].recv[last_set], count, config.dtype, config.redop, config.uniform_data, kSeed, nranks,
                                  -1, first, eps, ranks[r].wrong, ranks[r].max_abs, ranks[r].stream);
                 }
-                unsigned long long w = 0;
-                unsigned int m = 0;
-                B2_CUDA(cudaMemcpyAsync(&w, ranks[r].wrong, sizeof(w), cudaMemcpyDeviceToHost, ranks[r].stream));
-                B2_CUDA(cudaMemcpyAsync(&m, ranks[r].max_abs, sizeof(m), cudaMemcpyDeviceToHost, ranks[r].stream));
+                // Read the two counters back through pinned memory (a truly asynchronous copy).
+                unsigned long long* host = readback.get();
+                B2_CUDA(cudaMemcpyAsync(&host[0], ranks[r].wrong, sizeof(unsigned long long), cudaMemcpyDeviceToHost, ranks[r].stream));
+                B2_CUDA(cudaMemcpyAsync(&host[1], ranks[r].max_abs, sizeof(unsigned int), cudaMemcpyDeviceToHost, ranks[r].stream));
                 B2_CUDA(cudaStreamSynchronize(ranks[r].stream));
-                wrong_total += w;
+                wrong_total += host[0];
+                const unsigned int m = static_cast<unsigned int>(host[1] & 0xffffffffull);
                 float mf;
                 std::memcpy(&mf, &m, sizeof(mf));
                 max_abs = std::max(max_abs, mf);
@@ -322,15 +363,7 @@ int run_collective_bench(const BenchConfig& config, std::vector<BenchResult>* re
         }
         if (rc != 0) break;
     }
-    comm.reset();
-    for (int r = 0; r < nranks; ++r) {
-        DeviceGuard guard(ranks[r].device);
-        if (!config.loopback || r == 0) cudaStreamDestroy(ranks[r].stream);
-        cudaEventDestroy(ranks[r].start);
-        cudaEventDestroy(ranks[r].stop);
-        cudaFree(ranks[r].wrong);
-        cudaFree(ranks[r].max_abs);
-    }
+    comm.reset();  // waits for work in flight; streams, events and counters are released by their owners
     return rc;
 }
 

@@ -15,6 +15,8 @@ pytestmark = pytest.mark.gpu
     ["--collective", "reduce_scatter", "--nranks", "8", "--dtype", "fp16"],
     ["--collective", "all_gather", "--nranks", "8", "--algo", "ring"],
     ["--collective", "all_reduce", "--nranks", "4", "--transport", "shm"],
+    ["--collective", "all_reduce", "--nranks", "4", "--graph"],
+    ["--collective", "all_gather", "--nranks", "2", "--graph", "--symmetric"],
 ])
 def test_bench_cli_verifies(native_build, args):
     proc = run_native("b200ccl_collective_bench", "--loopback", *args, "-b", "1024", "-e", "4194304", "-f", "64", "-w", "1", "-n",
