@@ -9,9 +9,12 @@
 #     reference's NUMA calls into no-ops (its own fallback path); GPU code is unaffected.
 #   * libnvidia-ml at link time: the CUDA toolkit's stub; the driver's library is used at run time.
 #
-# usage: baseline/build_reference.sh [reference_dir] [out_dir]
+# Beside each benchmark binary it builds ref_e2e_n<N>, the harness of ref_e2e_driver.cu, against the
+# same unmodified static library.
+#
+# usage: baseline/build_reference.sh <reference_source_dir> [out_dir]
 set -euo pipefail
-REF=${1:-/root/reference}
+REF=${1:?usage: build_reference.sh <reference_source_dir> [out_dir]}
 HERE=$(cd "$(dirname "$0")" && pwd)
 OUT=${2:-$HERE/_ref}
 WORK=$(mktemp -d /tmp/ref_build.XXXXXX)
