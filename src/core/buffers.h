@@ -9,7 +9,9 @@
 #include "core/check.h"
 #include "core/numa.h"
 
+#include <cstdlib>
 #include <cstring>
+#include <new>
 #include <utility>
 
 namespace b200ccl {
@@ -73,19 +75,35 @@ public:
         release();
         if (count == 0) return;
         numa::PreferNode prefer(numa_node);
-        B2_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&ptr_), count * sizeof(T),
-                              cudaHostAllocMapped | cudaHostAllocPortable));
+        const cudaError_t st = cudaHostAlloc(reinterpret_cast<void**>(&ptr_), count * sizeof(T),
+                                             cudaHostAllocMapped | cudaHostAllocPortable);
+        if (st == cudaErrorNoDevice || st == cudaErrorInsufficientDriver) {
+            // No GPU in this process (host-only tests of proxies and edge wiring): ordinary memory.
+            (void)cudaGetLastError();
+            if (posix_memalign(reinterpret_cast<void**>(&ptr_), 4096, count * sizeof(T)) != 0) throw std::bad_alloc();
+            host_only_ = true;
+        } else {
+            B2_CUDA(st);
+        }
         std::memset(ptr_, 0, count * sizeof(T));  // also touches the pages under the preferred policy
         count_ = count;
     }
     T* get() const { return ptr_; }            // valid on host and, under unified addressing, on every GPU
     T& operator[](std::size_t i) const { return ptr_[i]; }
     std::size_t count() const { return count_; }
+    bool host_only() const { return host_only_; }
 private:
-    void release() { if (ptr_) cudaFreeHost(ptr_); ptr_ = nullptr; count_ = 0; }
-    void swap(MappedBuffer& o) { std::swap(ptr_, o.ptr_); std::swap(count_, o.count_); }
+    void release() {
+        if (ptr_) {
+            if (host_only_) std::free(ptr_);
+            else cudaFreeHost(ptr_);
+        }
+        ptr_ = nullptr; count_ = 0; host_only_ = false;
+    }
+    void swap(MappedBuffer& o) { std::swap(ptr_, o.ptr_); std::swap(count_, o.count_); std::swap(host_only_, o.host_only_); }
     T* ptr_ = nullptr;
     std::size_t count_ = 0;
+    bool host_only_ = false;
 };
 
 using MappedU64Array = MappedBuffer<unsigned long long>;
