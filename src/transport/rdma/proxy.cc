@@ -47,7 +47,8 @@ RdmaSendProxy::RdmaSendProxy(QueuePair* qp, CompletionQueue* cq, RdmaFifo fifo, 
 
 bool RdmaSendProxy::progress() { return guarded(static_cast<bool (RdmaProxy::*)()>(&RdmaSendProxy::body)); }
 
-bool RdmaSendProxy::drained() const { return failed() || next_complete_ >= load_acquire(send_tail_); }
+// Called from another thread than the one that drives progress(): reads only the atomic step.
+bool RdmaSendProxy::drained() const { return failed() || step() >= load_acquire(send_tail_); }
 
 bool RdmaSendProxy::body() {
     bool did = false;
