@@ -22,6 +22,7 @@
 #include "mem/ipc_window.h"
 #include "mem/symmetric.h"
 #include "sched/plan.h"
+#include "sched/transport_plan.h"
 #include "topo/topology.h"
 
 #include <algorithm>
@@ -52,7 +53,8 @@ public:
     int local_rank_count() const noexcept { return static_cast<int>(local_.size()); }
     int global_rank_count() const noexcept { return nranks_; }
     int first_global_rank() const noexcept { return local_.empty() ? 0 : local_[0].grank; }
-    TransportKind transport() const noexcept { return resolved_; }
+    // One kind when every ring edge has it, else mixed (e.g. peer memory inside processes, sockets between them).
+    TransportKind transport() const noexcept { return ring_plan_.resolved_kind(resolved_); }
     bool nvls_available() const noexcept { return alloc_ && alloc_->multicast_supported(); }
     std::vector<void*> alloc_symmetric(std::size_t bytes);
     void free_symmetric(const std::vector<void*>& ptrs);
@@ -104,6 +106,8 @@ private:
     std::size_t staging_half_ = 0;
     int channels_ = kDefaultChannels;
     sched::Tuning tuning_;
+    sched::ProcessLayout layout_;
+    sched::RingTransportPlan ring_plan_;
     topo::TopologyReport topo_;
     std::vector<Local> local_;
     std::unique_ptr<mem::SymmetricAllocator> alloc_;
@@ -170,11 +174,18 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
         bootstrap_->allgather(&mine, counts.data(), sizeof(int));
         for (int p = 0; p < bootstrap_->size(); ++p) {
             if (p < bootstrap_->rank()) first += counts[p];
+            layout_.first_rank.push_back(nranks_);
+            layout_.rank_count.push_back(counts[p]);
             nranks_ += counts[p];
         }
     } else {
         nranks_ = static_cast<int>(config.devices.size());
     }
+    if (layout_.first_rank.empty()) {
+        layout_.first_rank = {0};
+        layout_.rank_count = {nranks_};
+    }
+    layout_.nranks = nranks_;
     if (nranks_ < 1 || nranks_ > kMaxRanks)
         throw std::invalid_argument("communicator needs between 1 and " + std::to_string(kMaxRanks) +
                                     " ranks in total, got " + std::to_string(nranks_));
@@ -187,6 +198,15 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
 
     topo_ = topo::discover(config.devices);
     resolve_transport();
+    {
+        // Per-edge view of the ring: edges inside a process use peer memory (or host memory for
+        // shm); edges between processes use exported peer memory unless a network transport was
+        // asked for; a single process that asked for socket/rdma loops every edge through it.
+        const bool net = resolved_ == TransportKind::Socket || resolved_ == TransportKind::Rdma;
+        const TransportKind local_kind = resolved_ == TransportKind::Shm ? TransportKind::Shm : TransportKind::P2p;
+        ring_plan_ = sched::make_ring_transport_plan(layout_, local_kind, net ? resolved_ : TransportKind::P2p,
+                                                     net && !multiprocess_);
+    }
 
     // Peer-mapped memory exists for every transport except SHM, whose point is to work
     // without peer access (everything it shares lives in mapped host memory).
@@ -725,9 +745,7 @@ std::string Communicator::Impl::describe() const {
         os << "memory: mapped host memory only (shm)\n";
     for (const auto& l : local_) os << "rank " << l.grank << ": device " << l.device << "\n";
     os << topo_.text;
-    // Every rank reaches every other rank over the same kind of edge.
-    for (int a = 0; a < nranks_; ++a)
-        os << "edge " << a << "->" << (a + 1) % nranks_ << ": " << transport_name(resolved_) << "\n";
+    os << ring_plan_.describe();
     return os.str();
 }
 

@@ -7,6 +7,7 @@
 #include "collective/validate.h"
 #include "core/env.h"
 #include "sched/plan.h"
+#include "sched/transport_plan.h"
 
 #include <cstring>
 
@@ -93,6 +94,42 @@ int main() {
     T_CHECK(plan.stage_in && plan.stage_out && plan.algo == Algo::TwoShot);
     s.ring_only = true;
     T_CHECK(sched::make_plan(s, Algo::Auto, sched::default_tuning()).algo == Algo::Ring);
+    // process layouts and per-edge transport plans (synthetic 2x2 topologies, as the reference's
+    // tests/public_api.cu --topology mode and tests/p2p_topology.cu do)
+    sched::ProcessLayout two_by_two;
+    two_by_two.nranks = 4;
+    two_by_two.first_rank = {0, 2};
+    two_by_two.rank_count = {2, 2};
+    two_by_two.validate();
+    T_CHECK(two_by_two.distributed() && two_by_two.owner_of(1) == 0 && two_by_two.owner_of(2) == 1 && two_by_two.owner_of(9) == -1);
+    auto tp = sched::make_ring_transport_plan(two_by_two, TransportKind::P2p, TransportKind::Socket, false);
+    T_CHECK(tp.edge_kinds.size() == 4);
+    T_CHECK(tp.edge_kinds[0] == TransportKind::P2p && tp.edge_kinds[1] == TransportKind::Socket);   // 1->2 crosses
+    T_CHECK(tp.edge_kinds[2] == TransportKind::P2p && tp.edge_kinds[3] == TransportKind::Socket);   // 3->0 crosses
+    T_CHECK(tp.resolved_kind() == TransportKind::Mixed);
+    T_CHECK(tp.describe().find("edge 1->2: socket") != std::string::npos && tp.describe().find("edge 3->0: socket") != std::string::npos);
+    tp = sched::make_ring_transport_plan(two_by_two, TransportKind::P2p, TransportKind::P2p, false);
+    T_CHECK(tp.resolved_kind() == TransportKind::P2p);
+    tp = sched::make_ring_transport_plan(two_by_two, TransportKind::Shm, TransportKind::Rdma, false);
+    T_CHECK(tp.resolved_kind() == TransportKind::Mixed && tp.edge_kinds[0] == TransportKind::Shm && tp.edge_kinds[1] == TransportKind::Rdma);
+    sched::ProcessLayout one;
+    one.nranks = 4; one.first_rank = {0}; one.rank_count = {4};
+    T_CHECK(!one.distributed());
+    T_CHECK(sched::make_ring_transport_plan(one, TransportKind::Shm, TransportKind::P2p, false).resolved_kind() == TransportKind::Shm);
+    T_CHECK(sched::make_ring_transport_plan(one, TransportKind::P2p, TransportKind::Rdma, true).resolved_kind() == TransportKind::Rdma);
+    sched::ProcessLayout four_by_one;
+    four_by_one.nranks = 4; four_by_one.first_rank = {0, 1, 2, 3}; four_by_one.rank_count = {1, 1, 1, 1};
+    T_CHECK(sched::make_ring_transport_plan(four_by_one, TransportKind::P2p, TransportKind::Socket, false).resolved_kind() == TransportKind::Socket);
+    sched::ProcessLayout solo;
+    solo.nranks = 1; solo.first_rank = {0}; solo.rank_count = {1};
+    T_CHECK(sched::make_ring_transport_plan(solo, TransportKind::P2p, TransportKind::P2p, false).resolved_kind(TransportKind::P2p) == TransportKind::P2p);
+    sched::ProcessLayout gap = two_by_two;
+    gap.first_rank = {0, 3};
+    t_expect_throw([&] { gap.validate(); }, "do not follow", "gap in ranks");
+    gap = two_by_two; gap.nranks = 5;
+    t_expect_throw([&] { gap.validate(); }, "own 4 ranks", "sum mismatch");
+    t_expect_throw([&] { sched::make_ring_transport_plan(two_by_two, TransportKind::Socket, TransportKind::P2p, false); }, "inside a process", "local kind");
+    t_expect_throw([&] { sched::make_ring_transport_plan(two_by_two, TransportKind::P2p, TransportKind::Shm, false); }, "between processes", "cross kind");
     std::puts("validate ok");
     return 0;
 }
