@@ -77,7 +77,8 @@ int b2_comm_unregister(b2_comm* comm, void* const* ptrs);
 
 /* Planner (pure function, no GPU needed): out = {algo, grid, stage_in, stage_out, gather_mode}.
  * flags bits: 1 wide, 2 peers_read_input, 4 peers_write_output, 8 input_multicast,
- * 16 output_multicast, 32 in_place, 64 ring_only. Returns 2 with a message when impossible. */
+ * 16 output_multicast, 32 in_place, 64 ring_only, 128 word_aligned. The tuning is the default one
+ * with the B200CCL_* overrides of the environment. Returns 2 with a message when impossible. */
 int b2_make_plan(int collective, int dtype, int redop, int nranks, size_t count, unsigned flags, int forced_algo,
                  int out[5]);
 

@@ -29,7 +29,8 @@ enum class Collective : int { AllReduce = 0, ReduceScatter = 1, AllGather = 2 };
 //   TwoShot  rank r reduces shard r from all peers, then stores it into every peer's output
 //   Nvls     NVSwitch multicast: multimem.ld_reduce on the own shard, multimem.st broadcast
 //   Ring     ring over per-edge Simple-protocol FIFOs (works over SHM / socket / RDMA edges)
-enum class Algo : int { Auto = 0, OneShot = 1, TwoShot = 2, Nvls = 3, Ring = 4 };
+//   LowLatency  flag-in-data exchange without barriers for messages up to 32 KiB (AllReduce only)
+enum class Algo : int { Auto = 0, OneShot = 1, TwoShot = 2, Nvls = 3, Ring = 4, LowLatency = 5 };
 
 const char* dtype_name(DType d);
 const char* redop_name(RedOp r);
@@ -51,7 +52,7 @@ std::size_t dtype_size(DType d);
 float dtype_default_epsilon(DType d);
 
 struct BenchConfig {
-    std::string algo = "auto";  // auto|oneshot|twoshot|nvls|ring  ("ring_simple" = ring)
+    std::string algo = "auto";  // auto|oneshot|twoshot|nvls|ring|ll  ("ring_simple" = ring)
     Collective collective = Collective::AllReduce;
     DType dtype = DType::Float;
     RedOp redop = RedOp::Sum;

@@ -199,7 +199,8 @@ int b2_make_plan(int collective, int dtype, int redop, int nranks, size_t count,
         s.output_multicast = flags & 16u;
         s.in_place = flags & 32u;
         s.ring_only = flags & 64u;
-        const sched::Plan p = sched::make_plan(s, static_cast<Algo>(forced_algo), sched::default_tuning());
+        s.word_aligned = flags & 128u;
+        const sched::Plan p = sched::make_plan(s, static_cast<Algo>(forced_algo), sched::tuning_from_env());
         if (!p.error.empty()) throw std::invalid_argument(p.error);
         out[0] = static_cast<int>(p.algo);
         out[1] = p.grid;

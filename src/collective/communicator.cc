@@ -19,6 +19,7 @@
 #include "core/env.h"
 #include "kernels/sm100/dev_types.h"
 #include "kernels/sm100/direct_collectives.h"
+#include "kernels/sm100/ll_allreduce.h"
 #include "mem/ipc_window.h"
 #include "mem/symmetric.h"
 #include "sched/plan.h"
@@ -90,6 +91,7 @@ private:
     void launch_reduce_ranks(const CollectiveArgs& args, std::vector<dev::CollArgs>& per_rank, bool wide,
                              bool nvls, int grid);
     void launch_gather_ranks(const CollectiveArgs& args, std::vector<dev::GatherArgs>& per_rank, int grid);
+    void launch_low_latency(const CollectiveArgs& args);
     bool direct_peer_pointers() const { return loopback_ || (!multiprocess_ && resolved_ == TransportKind::P2p); }
     void poison(const std::string& why) const {
         if (latched_.empty()) latched_ = why;
@@ -113,6 +115,7 @@ private:
     std::unique_ptr<mem::SymmetricAllocator> alloc_;
     std::unique_ptr<mem::SymmetricRegion> ctrl_;
     std::unique_ptr<mem::SymmetricRegion> stage_;
+    std::unique_ptr<mem::SymmetricRegion> ll_area_;  // receive slots of the low-latency kernel (first use)
     // A window is a buffer that exists on every rank and that every rank can address: a symmetric
     // allocation (with a multicast alias where available) or a registered ordinary buffer.
     struct Window {
@@ -284,6 +287,7 @@ Communicator::Impl::~Impl() {
     ring_.reset();
     windows_.clear();
     stage_.reset();
+    ll_area_.reset();
     ctrl_.reset();
     for (auto& l : local_) {
         if (l.done) cudaEventDestroy(l.done);
@@ -522,6 +526,10 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
     shape.nranks = nranks_;
     shape.count = args.count;
     shape.wide = wide;
+    shape.word_aligned = (args.count * esz) % 4 == 0 && args.count > 0;
+    for (std::size_t i = 0; i < local_.size(); ++i)
+        shape.word_aligned &= reinterpret_cast<std::uintptr_t>(args.send_buffers[i]) % 4 == 0 &&
+                              reinterpret_cast<std::uintptr_t>(args.recv_buffers[i]) % 4 == 0;
     shape.in_place = in_place;
     shape.peers_read_input = direct_peer_pointers() || in_sym;
     shape.peers_write_output = direct_peer_pointers() || out_sym;
@@ -586,12 +594,61 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
         return;
     }
 
+    if (plan.algo == Algo::LowLatency) {
+        launch_low_latency(args);
+        return;
+    }
     if (plan.stage_in || plan.stage_out) ensure_staging();
     switch (collective) {
         case Collective::AllReduce: launch_all_reduce(args, plan, wide, in_loc, out_loc); break;
         case Collective::ReduceScatter: launch_reduce_scatter(args, plan, wide, in_loc); break;
         case Collective::AllGather: launch_all_gather(args, plan, wide, in_loc, out_loc); break;
     }
+}
+
+// Low-latency AllReduce: the ranks exchange {data, call number} words through receive areas in
+// symmetric memory; the user's buffers are only touched by their own rank.
+void Communicator::Impl::launch_low_latency(const CollectiveArgs& args) {
+    if (!ll_area_) ll_area_ = alloc_->allocate(kernels::ll_area_bytes(nranks_), "low-latency slots");
+    std::vector<dev::LlArgs> per(local_.size());
+    for (std::size_t i = 0; i < local_.size(); ++i) {
+        dev::LlArgs& a = per[i];
+        std::memset(&a, 0, sizeof(a));
+        a.in = args.send_buffers[i];
+        a.out = args.recv_buffers[i];
+        for (int p = 0; p < nranks_; ++p) {
+            a.area[p] = static_cast<unsigned long long*>(ll_area_->rank_ptr(p));
+            a.ctrl[p] = static_cast<dev::ControlBlock*>(ctrl_->rank_ptr(p));
+        }
+        a.own_ctrl = a.ctrl[local_[i].grank];
+        a.status = local_[i].status;
+        a.timeout_ns = timeout_ns_;
+        a.nwords = static_cast<unsigned>(args.count * dtype_size(args.dtype) / 4);
+        a.scale = args.redop == RedOp::Avg ? 1.0f / static_cast<float>(nranks_) : 1.0f;
+        a.rank = local_[i].grank;
+        a.nranks = nranks_;
+    }
+    try {
+        if (loopback_) {
+            DeviceGuard guard(local_[0].device);
+            cudaStream_t stream = args.streams[0];
+            for (auto& l : local_) wait_previous(l, stream);
+            B2_CUDA(kernels::launch_ll_all_reduce(args.dtype, args.redop, per.data(), nranks_, stream));
+            for (auto& l : local_) record_done(l, stream);
+        } else {
+            for (std::size_t i = 0; i < local_.size(); ++i) {
+                DeviceGuard guard(local_[i].device);
+                wait_previous(local_[i], args.streams[i]);
+                B2_CUDA(kernels::launch_ll_all_reduce(args.dtype, args.redop, &per[i], 0, args.streams[i]));
+                record_done(local_[i], args.streams[i]);
+            }
+        }
+    } catch (const std::exception& e) {
+        poison(std::string("launch failed: ") + e.what());
+        throw;
+    }
+    last_.grid = dev::kLlCtas;
+    last_.block = dev::kBlockThreads;
 }
 
 void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sched::Plan& plan, bool wide,

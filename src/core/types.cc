@@ -43,6 +43,7 @@ const char* algo_name(Algo a) {
         case Algo::TwoShot: return "twoshot";
         case Algo::Nvls: return "nvls";
         case Algo::Ring: return "ring";
+        case Algo::LowLatency: return "ll";
     }
     return "unknown";
 }
@@ -94,8 +95,9 @@ bool parse_transport(const char* text, TransportKind* out) {
 bool parse_algo(const char* text, Algo* out) {
     static const std::pair<const char*, Algo> t[] = {
         {"auto", Algo::Auto},       {"oneshot", Algo::OneShot}, {"twoshot", Algo::TwoShot},
-        {"nvls", Algo::Nvls},       {"ring", Algo::Ring},       {"ring_simple", Algo::Ring}};
-    return parse_from(text, out, t, 6);
+        {"nvls", Algo::Nvls},       {"ring", Algo::Ring},       {"ring_simple", Algo::Ring},
+        {"ll", Algo::LowLatency}};
+    return parse_from(text, out, t, 7);
 }
 
 bool parse_collective(const char* text, Collective* out) {

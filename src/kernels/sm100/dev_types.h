@@ -15,6 +15,9 @@ namespace b200ccl::dev {
 constexpr int kMaxCtas = 160;       // flag rows per rank; one row per CTA index (148 SMs on B200)
 constexpr int kBlockThreads = 512;  // direct kernels
 constexpr int kRingMaxChannels = 32;
+constexpr int kLlCtas = 8;                  // the low-latency kernel always runs this many CTAs per rank
+constexpr unsigned kLlMaxBytes = 32u << 10; // largest message it takes
+constexpr unsigned kLlMaxWords = kLlMaxBytes / 4;
 
 // Per-rank control block. It lives in symmetric memory: every rank can store into every other
 // rank's block; each rank polls only its own.
@@ -32,6 +35,8 @@ struct ControlBlock {
     // record itself is then written with plain stores into host memory).
     unsigned int fail_once;
     unsigned int pad_[30];
+    // Low-latency AllReduce: calls seen so far by each of its (fixed number of) CTAs. Local only.
+    unsigned long long ll_epoch[kLlCtas];
     // Ring/Simple step counters. *_tail / *_head follow nano-nccl's ownership rule
     // (src/transport/p2p/p2p_step_counters.h:32-35): recv_tail and send_head are polled by this
     // rank and written by its neighbours; base steps persist progress between launches.
@@ -101,6 +106,22 @@ struct GatherArgs {
     int nranks;
     int mode;        // 0 push (store own block into every out), 1 pull (load every in), 2 nvls
     int pack_bytes;  // 16, 4, 2 or 1
+};
+
+// Low-latency (flag-in-data) AllReduce. Every rank owns a receive area of
+// 2 parities x nranks sources x kLlMaxWords slots of 8 bytes {4 data bytes, 4-byte call number}.
+struct LlArgs {
+    const void* in;              // local input (any device memory of this rank)
+    void* out;                   // local output
+    unsigned long long* area[kMaxRanks];  // every rank's receive area
+    ControlBlock* own_ctrl;
+    ControlBlock* ctrl[kMaxRanks];        // to raise every rank's abort word when a wait runs out
+    Status* status;
+    unsigned long long timeout_ns;
+    unsigned int nwords;         // 4-byte words in the message
+    float scale;
+    int rank;
+    int nranks;
 };
 
 // Arguments of every emulated rank, passed by value to a loopback launch.

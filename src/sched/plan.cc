@@ -6,6 +6,10 @@
 
 namespace b200ccl::sched {
 
+namespace {
+constexpr std::size_t kLlPlanMaxBytes = 32u << 10;  // capacity of the low-latency receive slots
+}
+
 Tuning default_tuning() {
     // Measured on 8x B200 (NVSwitch), float sum, CUDA-event timing, maximum over ranks
     // (tables under tuning/):
@@ -46,6 +50,7 @@ Tuning tuning_from_env() {
     t.nvls_unroll = static_cast<int>(env::get_int("B200CCL_NVLS_UNROLL", t.nvls_unroll));
     t.bytes_per_cta = env::get_bytes("B200CCL_BYTES_PER_CTA", t.bytes_per_cta);
     t.oneshot_bytes_per_cta = env::get_bytes("B200CCL_ONESHOT_BYTES_PER_CTA", t.oneshot_bytes_per_cta);
+    t.ll_max_bytes = std::min<std::size_t>(env::get_bytes("B200CCL_LL_MAX_BYTES", t.ll_max_bytes), kLlPlanMaxBytes);
     return t;
 }
 
@@ -132,6 +137,16 @@ Plan make_plan(const CallShape& s, Algo forced, const Tuning& t) {
     }
 
     // AllReduce
+    const bool ll_fits = s.word_aligned && bytes <= kLlPlanMaxBytes && s.nranks >= 2;
+    if (forced == Algo::LowLatency && !ll_fits) {
+        p.error = "algo ll takes 4-byte aligned all_reduce messages of at most 32 KiB";
+        return p;
+    }
+    if (forced == Algo::LowLatency || (forced == Algo::Auto && ll_fits && bytes <= t.ll_max_bytes)) {
+        p.algo = Algo::LowLatency;  // neither buffer needs to be peer-addressable: no staging
+        p.grid = 8;
+        return p;
+    }
     Algo algo = forced;
     if (algo == Algo::Auto) {
         if (nvls_ok && bytes >= t.nvls_min_bytes) algo = Algo::Nvls;

@@ -20,6 +20,7 @@ struct CallShape {
     int nranks = 1;
     std::size_t count = 0;       // the API's `count`
     bool wide = false;           // every pointer 16-byte aligned and every block a multiple of 16 bytes
+    bool word_aligned = false;   // every pointer 4-byte aligned and the message a multiple of 4 bytes
     bool peers_read_input = false;    // peers can load this call's input directly
     bool peers_write_output = false;  // peers can store into this call's output directly
     bool input_multicast = false;     // input has a multicast alias (NVLS ld_reduce possible)
@@ -50,6 +51,9 @@ struct Tuning {
     int nvls_unroll = 4;                           // multimem loads in flight per thread (B200CCL_NVLS_UNROLL)
     std::size_t bytes_per_cta = 0;                 // work given to one CTA before another is added
     std::size_t oneshot_bytes_per_cta = 0;         // one-shot reads every peer's copy: spread it thinner
+    // AllReduce messages up to this size use the low-latency kernel (0 = only when asked for;
+    // B200CCL_LL_MAX_BYTES; never above 32 KiB).
+    std::size_t ll_max_bytes = 0;
 };
 Tuning default_tuning();
 Tuning tuning_from_env();

@@ -62,6 +62,33 @@ def test_planner(lib):
     assert rc == 2 and b"nvls" in lib.b2_last_error()
 
 
+def test_planner_low_latency(lib, monkeypatch):
+    WIDE, RD, WR, WORD = 1, 2, 4, 128
+    monkeypatch.delenv("B200CCL_LL_MAX_BYTES", raising=False)
+    rc, p = _plan(lib, 0, 1024, WIDE | RD | WR | WORD)
+    assert rc == 0 and p[0] == 1  # off unless asked for
+    rc, p = _plan(lib, 0, 1024, WORD, forced=5)
+    assert rc == 0 and p[0] == 5 and p[1] == 8 and p[2] == 0 and p[3] == 0  # no staging even for private buffers
+    rc, p = _plan(lib, 0, 8192, WORD, forced=5)
+    assert rc == 0 and p[0] == 5  # 32 KiB of floats still fits
+    rc, p = _plan(lib, 0, 8193, WORD, forced=5)
+    assert rc == 2 and b"32 KiB" in lib.b2_last_error()
+    rc, p = _plan(lib, 0, 1024, WIDE, forced=5)
+    assert rc == 2  # not 4-byte aligned
+    rc, p = _plan(lib, 1, 1024, WIDE | RD | WR | WORD, forced=5)
+    assert rc == 0 and p[0] != 5  # all_reduce only
+    monkeypatch.setenv("B200CCL_LL_MAX_BYTES", "16K")
+    rc, p = _plan(lib, 0, 4096, WIDE | RD | WR | WORD)
+    assert rc == 0 and p[0] == 5
+    rc, p = _plan(lib, 0, 4097 + 3, WIDE | RD | WR | WORD)
+    assert rc == 0 and p[0] != 5  # above the threshold: the usual choice
+    monkeypatch.setenv("B200CCL_LL_MAX_BYTES", "1M")  # clamped to the slot capacity
+    rc, p = _plan(lib, 0, 8192, WIDE | RD | WR | WORD)
+    assert rc == 0 and p[0] == 5
+    rc, p = _plan(lib, 0, 16384, WIDE | RD | WR | WORD)
+    assert rc == 0 and p[0] != 5
+
+
 def test_no_gpu_is_a_loud_error(lib):
     import torch
     if torch.cuda.is_available():

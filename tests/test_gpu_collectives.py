@@ -87,6 +87,56 @@ def test_forced_algorithms_and_odd_sizes(comms, algo, dtype):
             assert (out.float() - ref).abs().max().item() <= DTYPES[dtype]
 
 
+@pytest.mark.parametrize("ranks", [2, 4, 8])
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_low_latency_all_reduce(comms, ranks, dtype):
+    # The flag-in-data kernel: sizes that change from call to call (so the two slot parities and
+    # the per-CTA call counters are exercised with different word ranges), every operator, in place.
+    comm = comms(ranks, algo="ll")
+    esz = torch.empty(0, dtype=dtype).element_size()
+    sizes = [4 // esz, 4096 // esz + 2, (32 << 10) // esz, 2, 1026, 8 // esz, (32 << 10) // esz]
+    for i, numel in enumerate(sizes):
+        op = ["sum", "avg", "max", "min"][i % 4]
+        inputs = make_inputs(ranks, numel, dtype, seed=100 + i)
+        ref = reference(inputs, op)
+        if i % 2:
+            outputs = inputs
+            comm.all_reduce(outputs, op=op)
+        else:
+            outputs = [torch.full_like(t, float("nan")) for t in inputs]
+            comm.all_reduce(outputs, inputs, op=op)
+        torch.cuda.synchronize()
+        comm.check_async_error()
+        info = comm.last_call()
+        assert info["algo"] == "ll" and info["grid"] == 8 and not info["staged_in"]
+        for out in outputs:
+            assert (out.float() - ref).abs().max().item() <= DTYPES[dtype], (numel, op)
+        for out in outputs[1:]:
+            assert torch.equal(out, outputs[0])
+
+
+def test_low_latency_limits_and_mixing(comms):
+    comm = comms(4, algo="ll")
+    big = make_inputs(4, (32 << 10) // 4 + 1, torch.float32, seed=1)
+    with pytest.raises(Exception, match="32 KiB"):
+        comm.all_reduce([torch.empty_like(t) for t in big], big)
+    odd = make_inputs(4, 3, torch.bfloat16, seed=1)  # 6 bytes: not a whole number of words
+    with pytest.raises(Exception, match="4-byte"):
+        comm.all_reduce([torch.empty_like(t) for t in odd], odd)
+    # Refused calls leave the communicator usable, and the kernel mixes freely with the others.
+    auto = comms(4)
+    for numel in (256, 1 << 16, 512):
+        inputs = make_inputs(4, numel, torch.float32, seed=numel)
+        ref = reference(inputs, "sum")
+        for c in (comm, auto) if numel <= 8192 else (auto,):
+            outputs = [torch.empty_like(t) for t in inputs]
+            c.all_reduce(outputs, inputs)
+            torch.cuda.synchronize()
+            c.check_async_error()
+            for out in outputs:
+                assert (out - ref).abs().max().item() <= DTYPES[torch.float32]
+
+
 @pytest.mark.parametrize("ranks", [2, 8])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 def test_reduce_scatter_and_all_gather(comms, ranks, dtype):
@@ -108,7 +158,7 @@ def test_reduce_scatter_and_all_gather(comms, ranks, dtype):
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
 @pytest.mark.parametrize("op", ["max", "min"])
-@pytest.mark.parametrize("algo", ["oneshot", "twoshot", "ring"])
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot", "ring", "ll"])
 def test_nan_propagates_through_max_and_min(comms, dtype, op, algo):
     # NaNs injected on rank 1 at indices 3, 11, 19, 27 of a 32-element message (the reference's
     # tests/public_api.cu:166-230 pattern); every dtype must return NaN exactly there.
