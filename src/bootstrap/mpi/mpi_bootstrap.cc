@@ -1,13 +1,18 @@
-// MPI adapter of the control plane. Compiled only with B200CCL_ENABLE_MPI=ON (the image this
-// library is developed on has no MPI; the TCP rendezvous is the default and is what the tests use).
+// MPI adapter of the control plane. Compiled only with B200CCL_ENABLE_MPI=ON (the TCP rendezvous is
+// the default). Where no MPI is installed the adapter is still compiled and run by
+// tests/cpp/fake_mpi/test_mpi_adapter.cc against an in-process stand-in for the few MPI calls it makes.
 // Only the MPI C API is used (no C++ bindings), as in the reference
 // (src/collective/all_reduce/mpi_communicator.cc; tests/mpi_c_api_link_static.py).
 #include "b200ccl/mpi.h"
 
 #if defined(B200CCL_ENABLE_MPI)
 
+#include "bootstrap/fd_exchange.h"
+
+#include <cstdint>
 #include <cstring>
 #include <stdexcept>
+#include <string>
 #include <vector>
 
 namespace b200ccl {
@@ -31,25 +36,25 @@ public:
         if (!initialized || finalized) throw std::runtime_error("MPI must be initialised and not finalised");
         mpi_check(MPI_Comm_rank(comm_, &rank_), "MPI_Comm_rank");
         mpi_check(MPI_Comm_size(comm_, &size_), "MPI_Comm_size");
-        // Descriptor passing needs AF_UNIX sockets; reuse the TCP rendezvous for that part, with
-        // the address published by rank 0 through MPI.
-        int port = 0;
-        if (rank_ == 0) port = 20000 + (static_cast<int>(::getpid()) % 20000);
-        mpi_check(MPI_Bcast(&port, 1, MPI_INT, 0, comm_), "MPI_Bcast");
-        fd_helper_ = create_tcp_bootstrap("127.0.0.1", port, rank_, size_);
     }
     int rank() const override { return rank_; }
     int size() const override { return size_; }
     void allgather(const void* in, void* out, std::size_t bytes) override {
+        if (bytes > static_cast<std::size_t>(INT32_MAX)) throw std::invalid_argument("MPI bootstrap: blob too large");
         mpi_check(MPI_Allgather(in, static_cast<int>(bytes), MPI_BYTE, out, static_cast<int>(bytes), MPI_BYTE, comm_), "MPI_Allgather");
     }
     void barrier() override { mpi_check(MPI_Barrier(comm_), "MPI_Barrier"); }
-    std::vector<std::vector<int>> exchange_fds(const std::vector<int>& fds) override { return fd_helper_->exchange_fds(fds); }
+    // Descriptors cannot travel through MPI: they go over AF_UNIX sockets whose names are agreed
+    // through this object's own all-gather.
+    std::vector<std::vector<int>> exchange_fds(const std::vector<int>& fds) override {
+        if (!fdx_) fdx_.reset(new FdExchange(*this, 60000));
+        return fdx_->exchange(fds);
+    }
 
 private:
     MPI_Comm comm_;
     int rank_ = 0, size_ = 1;
-    std::unique_ptr<Bootstrap> fd_helper_;
+    std::unique_ptr<FdExchange> fdx_;
 };
 
 }  // namespace

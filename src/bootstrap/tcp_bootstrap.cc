@@ -1,9 +1,10 @@
-// TCP rendezvous: rank 0 is a star hub for all-gather/barrier; descriptor passing uses one
-// abstract AF_UNIX listener per process. This is the default control plane; it plays the role
+// TCP rendezvous: rank 0 is a star hub for all-gather/barrier; descriptor passing is done by
+// FdExchange (one abstract AF_UNIX listener per process). This is the default control plane; it plays the role
 // that the MPI C API plays for nano-nccl (src/collective/all_reduce/mpi_communicator.cc:
 // 134-155 rank layout, 38-75 error consensus, 203-208 address all-gather).
 #include "b200ccl/bootstrap.h"
 
+#include "bootstrap/fd_exchange.h"
 #include "core/check.h"
 
 #include <arpa/inet.h>
@@ -63,14 +64,6 @@ void read_all(int fd, void* buf, std::size_t n, int timeout_ms) {
     }
 }
 
-struct FdHeader {
-    int32_t src_rank;
-    int32_t nfds;
-    uint32_t seq;
-    uint32_t valid_mask_lo;  // bit i set → entry i carries a descriptor (nfds ≤ 32 per call)
-};
-
-constexpr int kMaxFdsPerCall = 32;
 
 class TcpBootstrap final : public Bootstrap {
 public:
@@ -86,7 +79,6 @@ public:
         for (int fd : clients_) if (fd >= 0) ::close(fd);
         if (root_fd_ >= 0) ::close(root_fd_);
         if (listen_fd_ >= 0) ::close(listen_fd_);
-        if (unix_fd_ >= 0) ::close(unix_fd_);
     }
 
     int rank() const override { return rank_; }
@@ -115,19 +107,8 @@ public:
     }
 
     std::vector<std::vector<int>> exchange_fds(const std::vector<int>& fds) override {
-        const int nf = static_cast<int>(fds.size());
-        if (nf > kMaxFdsPerCall) throw std::invalid_argument("bootstrap: too many descriptors in one exchange");
-        std::vector<std::vector<int>> result(size_, std::vector<int>(nf, -1));
-        for (int i = 0; i < nf; ++i) result[rank_][i] = fds[i] >= 0 ? ::dup(fds[i]) : -1;
-        if (size_ == 1) return result;
-        ensure_unix_listener();
-        ++seq_;
-        for (int p = 0; p < size_; ++p) {
-            if (p != rank_) send_fds_to(p, fds);
-        }
-        for (int k = 0; k < size_ - 1; ++k) recv_fds(&result, nf);
-        barrier();  // nobody starts the next exchange while a peer still accepts this one
-        return result;
+        if (!fdx_) fdx_.reset(new FdExchange(*this, timeout_ms_));
+        return fdx_->exchange(fds);
     }
 
 private:
@@ -192,136 +173,13 @@ private:
         write_all(root_fd_, &r, sizeof(r));
     }
 
-    static sockaddr_un unix_addr(uint64_t token, int rank, socklen_t* len) {
-        sockaddr_un sa{};
-        sa.sun_family = AF_UNIX;
-        char name[96];
-        const int n = std::snprintf(name, sizeof(name), "b200ccl-%016llx-%d",
-                                    static_cast<unsigned long long>(token), rank);
-        sa.sun_path[0] = '\0';  // abstract namespace: no file to clean up
-        std::memcpy(sa.sun_path + 1, name, static_cast<std::size_t>(n));
-        *len = static_cast<socklen_t>(offsetof(sockaddr_un, sun_path) + 1 + n);
-        return sa;
-    }
-
-    void ensure_unix_listener() {
-        if (unix_fd_ >= 0) return;
-        uint64_t token = 0;
-        if (rank_ == 0) {
-            std::random_device rd;
-            token = (static_cast<uint64_t>(rd()) << 32) ^ rd() ^ (static_cast<uint64_t>(::getpid()) << 20);
-        }
-        std::vector<uint64_t> all(size_);
-        allgather(&token, all.data(), sizeof(token));
-        token_ = all[0];
-        unix_fd_ = ::socket(AF_UNIX, SOCK_STREAM, 0);
-        if (unix_fd_ < 0) fail("socket(AF_UNIX)");
-        socklen_t len = 0;
-        sockaddr_un sa = unix_addr(token_, rank_, &len);
-        if (::bind(unix_fd_, reinterpret_cast<sockaddr*>(&sa), len) != 0) fail("bind(AF_UNIX)");
-        if (::listen(unix_fd_, size_ + 8) != 0) fail("listen(AF_UNIX)");
-        barrier();  // every listener exists before anyone connects
-    }
-
-    void send_fds_to(int peer, const std::vector<int>& fds) {
-        const int fd = ::socket(AF_UNIX, SOCK_STREAM, 0);
-        if (fd < 0) fail("socket(AF_UNIX)");
-        socklen_t len = 0;
-        sockaddr_un sa = unix_addr(token_, peer, &len);
-        if (::connect(fd, reinterpret_cast<sockaddr*>(&sa), len) != 0) {
-            ::close(fd);
-            fail("connect(AF_UNIX) to rank " + std::to_string(peer));
-        }
-        FdHeader h{};
-        h.src_rank = rank_;
-        h.nfds = static_cast<int32_t>(fds.size());
-        h.seq = seq_;
-        std::vector<int> valid;
-        for (std::size_t i = 0; i < fds.size(); ++i) {
-            if (fds[i] >= 0) {
-                h.valid_mask_lo |= (1u << i);
-                valid.push_back(fds[i]);
-            }
-        }
-        msghdr msg{};
-        iovec iov{&h, sizeof(h)};
-        msg.msg_iov = &iov;
-        msg.msg_iovlen = 1;
-        alignas(cmsghdr) char ctrl[CMSG_SPACE(sizeof(int) * kMaxFdsPerCall)];
-        if (!valid.empty()) {
-            std::memset(ctrl, 0, sizeof(ctrl));
-            msg.msg_control = ctrl;
-            msg.msg_controllen = CMSG_SPACE(sizeof(int) * valid.size());
-            cmsghdr* c = CMSG_FIRSTHDR(&msg);
-            c->cmsg_level = SOL_SOCKET;
-            c->cmsg_type = SCM_RIGHTS;
-            c->cmsg_len = CMSG_LEN(sizeof(int) * valid.size());
-            std::memcpy(CMSG_DATA(c), valid.data(), sizeof(int) * valid.size());
-        }
-        if (::sendmsg(fd, &msg, MSG_NOSIGNAL) != static_cast<ssize_t>(sizeof(h))) {
-            ::close(fd);
-            fail("sendmsg(SCM_RIGHTS)");
-        }
-        ::close(fd);
-    }
-
-    void recv_fds(std::vector<std::vector<int>>* result, int nf) {
-        pollfd pfd{unix_fd_, POLLIN, 0};
-        const int pr = ::poll(&pfd, 1, timeout_ms_);
-        if (pr <= 0) throw std::runtime_error("bootstrap: timed out waiting for descriptors");
-        const int fd = ::accept(unix_fd_, nullptr, nullptr);
-        if (fd < 0) fail("accept(AF_UNIX)");
-        FdHeader h{};
-        msghdr msg{};
-        iovec iov{&h, sizeof(h)};
-        msg.msg_iov = &iov;
-        msg.msg_iovlen = 1;
-        alignas(cmsghdr) char ctrl[CMSG_SPACE(sizeof(int) * kMaxFdsPerCall)];
-        msg.msg_control = ctrl;
-        msg.msg_controllen = sizeof(ctrl);
-        pollfd dfd{fd, POLLIN, 0};
-        if (::poll(&dfd, 1, timeout_ms_) <= 0) {
-            ::close(fd);
-            throw std::runtime_error("bootstrap: timed out reading descriptors");
-        }
-        const ssize_t got = ::recvmsg(fd, &msg, MSG_WAITALL);
-        ::close(fd);
-        if (got != static_cast<ssize_t>(sizeof(h))) fail("recvmsg(SCM_RIGHTS)");
-        std::vector<int> valid;
-        for (cmsghdr* c = CMSG_FIRSTHDR(&msg); c; c = CMSG_NXTHDR(&msg, c)) {
-            if (c->cmsg_level == SOL_SOCKET && c->cmsg_type == SCM_RIGHTS) {
-                const std::size_t k = (c->cmsg_len - CMSG_LEN(0)) / sizeof(int);
-                valid.resize(k);
-                std::memcpy(valid.data(), CMSG_DATA(c), k * sizeof(int));
-            }
-        }
-        auto close_all = [&] { for (int v : valid) ::close(v); };
-        if (h.src_rank < 0 || h.src_rank >= size_ || h.src_rank == rank_ || h.nfds != nf || h.seq != seq_) {
-            close_all();
-            throw std::runtime_error("bootstrap: descriptor exchange out of step with rank " +
-                                     std::to_string(h.src_rank));
-        }
-        std::size_t vi = 0;
-        for (int i = 0; i < nf; ++i) {
-            if (h.valid_mask_lo & (1u << i)) {
-                if (vi >= valid.size()) {
-                    close_all();
-                    throw std::runtime_error("bootstrap: fewer descriptors arrived than announced");
-                }
-                (*result)[h.src_rank][i] = valid[vi++];
-            }
-        }
-    }
-
     int rank_;
     int size_;
     int timeout_ms_;
     int listen_fd_ = -1;
     int root_fd_ = -1;
     std::vector<int> clients_;
-    int unix_fd_ = -1;
-    uint64_t token_ = 0;
-    uint32_t seq_ = 0;
+    std::unique_ptr<FdExchange> fdx_;
 };
 
 }  // namespace

@@ -97,7 +97,7 @@ SelfTestResult selftest_abort(int device, double timeout_ms) {
                                         s.started, s.ok);
     B2_CUDA(cudaGetLastError());
     // Raise the abort word once the kernel says it is waiting (or after a grace period: the
-    // kernel's own budget ends the wait in any case).
+    // kernel's own time limit ends the wait in any case).
     const auto t0 = std::chrono::steady_clock::now();
     while (__atomic_load_n(s.started, __ATOMIC_ACQUIRE) == 0u &&
            std::chrono::steady_clock::now() - t0 < std::chrono::milliseconds(static_cast<long>(timeout_ms / 2)))

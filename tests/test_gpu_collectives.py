@@ -276,7 +276,7 @@ def test_bounded_wait_reports_instead_of_hanging():
     _lib.check(lib.b2_selftest_wait(0, 0, 100.0, out, ctypes.byref(waited)))
     assert out[0] == 0 and out[1] == 1 and out[2] == 99 and out[3] == 1
     assert 90.0 <= waited.value <= 1000.0
-    # The host raises the abort word while a kernel waits with a 2 s budget: ends early as ABORTED (2).
+    # The host raises the abort word while a kernel waits with a 2 s limit: ends early as ABORTED (2).
     _lib.check(lib.b2_selftest_wait(1, 0, 2000.0, out, ctypes.byref(waited)))
     assert out[0] == 0 and out[1] in (1, 2)
     if out[1] == 2:
