@@ -88,6 +88,11 @@ int b2_make_plan(int collective, int dtype, int redop, int nranks, size_t count,
 int b2_ring_sim(const long long cfg[6], size_t count, size_t fifo_bytes, double wait_timeout_ms, long long out_i[7],
                 double out_d[2]);
 
+/* CPU simulator of the low-latency AllReduce protocol (no GPU needed). cfg: {nranks, ctas, lanes, redop,
+ * max_words, slow_rank, stall_rank, stall_at_call}; call_words[ncalls]: words per call;
+ * out: {wrong, timed_out, timeout_rank, timeout_peer, timeout_call, max_lead}. */
+int b2_ll_sim(const long long cfg[8], const size_t* call_words, int ncalls, double wait_timeout_ms, long long out[6]);
+
 /* Single-GPU self-tests of the signalling primitives (bounded; they cannot hang the device).
  * kind 0: a wait on a flag nothing sets must time out; kind 1: the host raises the abort word
  * while a kernel waits. out = {wait_ok, status_code, where, abort_raised}; *waited_ms as measured

@@ -4,6 +4,7 @@
 #include "b200ccl/communicator.h"
 #include "kernels/sm100/selftest.h"
 #include "sched/plan.h"
+#include "sim/ll_sim.h"
 #include "sim/ring_sim.h"
 
 #include <cstring>
@@ -207,6 +208,30 @@ int b2_make_plan(int collective, int dtype, int redop, int nranks, size_t count,
         out[2] = p.stage_in;
         out[3] = p.stage_out;
         out[4] = p.gather_mode;
+    });
+}
+
+int b2_ll_sim(const long long cfg[8], const size_t* call_words, int ncalls, double wait_timeout_ms, long long out[6]) {
+    return guarded([&] {
+        sim::LlSimConfig c;
+        c.nranks = static_cast<int>(cfg[0]);
+        c.ctas = static_cast<int>(cfg[1]);
+        c.lanes = static_cast<int>(cfg[2]);
+        c.redop = static_cast<RedOp>(cfg[3]);
+        c.max_words = static_cast<std::size_t>(cfg[4]);
+        c.slow_rank = static_cast<int>(cfg[5]);
+        c.stall_rank = static_cast<int>(cfg[6]);
+        c.stall_at_call = static_cast<int>(cfg[7]);
+        c.wait_timeout_ms = wait_timeout_ms;
+        c.call_words.assign(call_words, call_words + (ncalls > 0 ? ncalls : 0));
+        const sim::LlSimResult r = sim::run_ll_sim(c);
+        if (r.wrong < 0) throw std::invalid_argument(r.message);
+        out[0] = r.wrong;
+        out[1] = r.timed_out;
+        out[2] = r.timeout_rank;
+        out[3] = r.timeout_peer;
+        out[4] = r.timeout_call;
+        out[5] = r.max_lead;
     });
 }
 

@@ -67,3 +67,14 @@ def test_stopped_rank_is_detected(lib):
     assert r["timed_out"] == 1
     assert r["timeout_peer"] == 2 or r["timeout_rank"] != 2
     assert r["timeout_rank"] in (0, 1, 3)
+
+
+def test_low_latency_protocol_sim():
+    # The flag-in-data AllReduce on host threads: lengths change from call to call, one rank lags.
+    from nano_nccl_b200.utils import ll_sim
+    r = ll_sim([1, 1000, 7, 1024, 3, 512] * 10, nranks=8, ctas=2, redop="avg", slow_rank=3)
+    assert r["wrong"] == 0 and not r["timed_out"] and r["max_lead"] <= 1
+    r = ll_sim([64] * 8, nranks=4, stall_rank=1, stall_at_call=5, wait_timeout_ms=200.0)
+    assert r["timed_out"] == 1 and r["timeout_peer"] == 1 and r["timeout_call"] == 5 and r["wrong"] == 0
+    with pytest.raises(ValueError):
+        ll_sim([4096], max_words=1024)
