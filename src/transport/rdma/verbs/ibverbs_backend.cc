@@ -1,6 +1,7 @@
-// libibverbs implementation of VerbsBackend. Compiled only with B200CCL_ENABLE_RDMA_VERBS=ON
-// (the machines this library is developed and tested on have neither an HCA nor the verbs headers,
-// so this file is NOT exercised by the test-suite; the proxies above it are tested against FakeVerbs).
+// libibverbs implementation of VerbsBackend. Part of the library only with B200CCL_ENABLE_RDMA_VERBS=ON.
+// Where libibverbs is not installed it is still compiled and run by
+// tests/cpp/fake_ibverbs/test_ibverbs_backend.cc against a stand-in header with an in-process loopback
+// fabric (no HCA); it has not been run on real hardware.
 //
 // Parity: nano-nccl src/transport/rdma/rdma_endpoint.cc:27-37, 41-80, 164-248 (device choice by
 // interface name through sysfs or by GID == the interface's IPv6/IPv4-mapped address, port 1 must be
@@ -17,6 +18,7 @@
 
 #include <infiniband/verbs.h>
 
+#include <arpa/inet.h>
 #include <cstring>
 #include <fstream>
 #include <stdexcept>
