@@ -66,3 +66,73 @@ def test_step_counters_use_system_scope_release_acquire():
     # data stores of the whole CTA are ordered before the counter by a block barrier, then release
     publish = ring[ring.index("// Publish:"):]
     assert publish.index("__syncthreads()") < publish.index("st_release_sys(st.ch.recv_head") < publish.index("st_release_sys(st.ch.send_tail")
+
+
+def test_low_latency_kernel_waits_are_bounded_and_flags_travel_with_the_data():
+    ll = read(os.path.join(KERNELS, "ll_allreduce.cu"))
+    # one 8-byte store carries data and call number; one 8-byte load polls them
+    assert "st.relaxed.sys.global.v2.u32" in ll and "ld.relaxed.sys.global.v2.u32" in ll
+    spin = ll[ll.index("while (v.y != flag)"):]
+    spin = spin[:spin.index("float f[")]
+    assert "abort_flag" in spin and "timeout_ns" in spin and "kStatusTimeout" in spin and spin.count("break;") >= 2
+    assert "cooperative" in ll.lower(), "emulated ranks wait on one another: they must share one cooperative launch"
+
+
+def test_bench_profiling_is_off_by_default_and_starts_after_warm_up():
+    # Same contract as the reference's tests/bench_profiling_static.py: numbers never come from an
+    # instrumented build, and the profiler window excludes warm-up.
+    cmake = read(os.path.join(ROOT, "CMakeLists.txt"))
+    assert re.search(r"option\(B200CCL_ENABLE_BENCH_PROFILING [^)]* OFF\)", cmake)
+    assert re.search(r"option\(B200CCL_ENABLE_TIMELINE [^)]* OFF\)", cmake)
+    runner = read(os.path.join(ROOT, "src", "collective", "bench_runner.cu"))
+    assert runner.index("config.warmup_iters") < runner.index("ProfilerSession session")
+    prof = read(os.path.join(ROOT, "src", "collective", "bench_profiling.h"))
+    assert "#if defined(B200CCL_ENABLE_BENCH_PROFILING)" in prof and "cudaProfilerStart" in prof
+
+
+def test_only_sm_100a_is_built():
+    cmake = read(os.path.join(ROOT, "CMakeLists.txt"))
+    assert cmake.count("-gencode") == 1 and "arch=compute_100a,code=sm_100a" in cmake and "-lineinfo" in cmake
+    assert 'NOT B200CCL_CUDA_ARCH STREQUAL "100a"' in cmake and "FATAL_ERROR" in cmake
+    entry = read(os.path.join(ROOT, "__graft_entry__.py"))
+    assert "sm_100a" in entry or "cmake" in entry
+
+
+def test_mpi_adapter_uses_the_c_api_only():
+    # tests/mpi_c_api_link_static.py of the reference: no C++ bindings, C component only.
+    adapter = read(os.path.join(ROOT, "src", "bootstrap", "mpi", "mpi_bootstrap.cc"))
+    assert "MPI::" not in adapter and "mpicxx" not in adapter
+    cmake = read(os.path.join(ROOT, "CMakeLists.txt"))
+    assert "find_package(MPI REQUIRED COMPONENTS C)" in cmake and "MPI::MPI_C" in cmake and "MPI_CXX" not in cmake
+
+
+def test_rdma_proxy_contracts():
+    proxy = read(os.path.join(ROOT, "src", "transport", "rdma", "proxy.cc"))
+    backend = read(os.path.join(ROOT, "src", "transport", "rdma", "verbs", "ibverbs_backend.cc"))
+    header = read(os.path.join(ROOT, "src", "transport", "rdma", "verbs_backend.h"))
+    gdr = read(os.path.join(ROOT, "src", "transport", "rdma", "gdr.cc"))
+    # multi-flight with selective signalling; the queue pair never signals everything
+    assert "max_flight()" in proxy and "kSignalEvery" in proxy and "window_full" in proxy and "burst_tail" in proxy
+    assert "init.sq_sig_all = 0" in backend and "kMaxInlineData = 64" in header
+    # the payload goes out straight from the FIFO slot: no bounce copy anywhere in the send path
+    assert "wr.local_addr = fifo_.data + slot * fifo_.slot_bytes" in proxy and "wr.lkey = fifo_.mr.lkey" in proxy
+    send_path = proxy[proxy.index("// 2. Post what the kernel has published"):proxy.index("qp_->post_send(wr);")]
+    assert "memcpy" not in send_path
+    # zero-byte slices never reach the network
+    assert proxy.count("zero_payload_posts_.fetch_add") >= 2
+    # WRITE plane: the grant is cleared at post time and goes inline; payloads carry their size as immediate data
+    assert "WrOpcode::RdmaWriteWithImm" in proxy and "wr.imm = bytes" in proxy and "wr.inline_data = true" in proxy
+    assert proxy.index("wr.imm = bytes") < proxy.index("__atomic_store_n(&grant.ready, 0u") < proxy.index("qp_->post_send(wr);")
+    # device-memory FIFOs: registration failure is an error, never a silent host fallback
+    gdr_branch = gdr[gdr.index("FifoPlacement::Gdr"):gdr.index("} else {")]
+    assert "register_device_memory" in gdr_branch and "host_" not in gdr_branch
+    assert "ibv_reg_dmabuf_mr" in backend and "unavailable" in backend
+
+
+def test_transport_kinds_and_parser_contract():
+    types_h = read(os.path.join(ROOT, "include", "b200ccl", "types.h"))
+    assert re.search(r"enum class TransportKind[^}]*Socket[^}]*Rdma[^}]*Mixed", types_h)
+    types_cc = read(os.path.join(ROOT, "src", "core", "types.cc"))
+    parse = types_cc[types_cc.index("bool parse_transport"):]
+    parse = parse[:parse.index("\n}\n")]
+    assert '"rdma"' in parse and '"socket"' not in parse and '"mixed"' not in parse
