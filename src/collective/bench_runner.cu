@@ -6,9 +6,11 @@
 #include "core/buffers.h"
 #include "core/check.h"
 #include "core/datagen.h"
+#include "core/env.h"
 #include "core/stream.h"
 
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <memory>
@@ -62,6 +64,53 @@ __global__ void verify_kernel(const typename DTypeTraits<D>::type* out, std::siz
 
 int grid_for(std::size_t count) {
     return static_cast<int>(std::min<std::size_t>((count + 255) / 256, 148 * 8));
+}
+
+// Debug aid (B200CCL_DEBUG_FIRST_WRONG=1, as NANO_NCCL_DEBUG_FIRST_WRONG in the reference's
+// ring_simple.cu:80, 91-95): after a failed verification, find the first mismatching element on the
+// host and print it. Runs only when something is already wrong.
+template <DType D>
+void report_first_wrong_t(const void* device_out, std::size_t count, RedOp op, bool uniform, std::uint64_t seed, int nranks,
+                          int src_rank, std::uint64_t first, float eps, int rank) {
+    using T = typename DTypeTraits<D>::type;
+    std::vector<T> host(count);
+    if (cudaMemcpy(host.data(), device_out, count * sizeof(T), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return;
+    }
+    auto input = [&](int r, std::uint64_t i) {
+        return static_cast<double>(DTypeTraits<D>::to_float(DTypeTraits<D>::from_float(datagen::value(uniform, seed, r, i))));
+    };
+    for (std::size_t i = 0; i < count; ++i) {
+        double expect;
+        if (src_rank >= 0) {
+            expect = input(src_rank, first + i);
+        } else {
+            expect = input(0, first + i);
+            for (int r = 1; r < nranks; ++r) {
+                const double v = input(r, first + i);
+                if (op == RedOp::Max) expect = v > expect ? v : expect;
+                else if (op == RedOp::Min) expect = v < expect ? v : expect;
+                else expect += v;
+            }
+            if (op == RedOp::Avg) expect /= nranks;
+        }
+        const float got = DTypeTraits<D>::to_float(host[i]);
+        if (!(std::fabs(got - static_cast<float>(expect)) <= eps)) {
+            std::fprintf(stderr, "first wrong element: rank %d index %zu got %.9g expected %.9g (eps %g)\n", rank, i,
+                         static_cast<double>(got), expect, static_cast<double>(eps));
+            return;
+        }
+    }
+}
+
+void report_first_wrong(const void* out, std::size_t count, DType dtype, RedOp op, bool uniform, std::uint64_t seed,
+                        int nranks, int src_rank, std::uint64_t first, float eps, int rank) {
+    switch (dtype) {
+        case DType::Float: report_first_wrong_t<DType::Float>(out, count, op, uniform, seed, nranks, src_rank, first, eps, rank); break;
+        case DType::Float16: report_first_wrong_t<DType::Float16>(out, count, op, uniform, seed, nranks, src_rank, first, eps, rank); break;
+        case DType::BFloat16: report_first_wrong_t<DType::BFloat16>(out, count, op, uniform, seed, nranks, src_rank, first, eps, rank); break;
+    }
 }
 
 }  // namespace
@@ -321,6 +370,17 @@ int run_collective_bench(const BenchConfig& config, std::vector<BenchResult>* re
                 B2_CUDA(cudaMemcpyAsync(&host[0], ranks[r].wrong, sizeof(unsigned long long), cudaMemcpyDeviceToHost, ranks[r].stream));
                 B2_CUDA(cudaMemcpyAsync(&host[1], ranks[r].max_abs, sizeof(unsigned int), cudaMemcpyDeviceToHost, ranks[r].stream));
                 B2_CUDA(cudaStreamSynchronize(ranks[r].stream));
+                if (host[0] != 0 && wrong_total == 0 && env::get_bool("B200CCL_DEBUG_FIRST_WRONG", false, "NANO_NCCL_DEBUG_FIRST_WRONG")) {
+                    if (coll == Collective::AllGather) {
+                        for (int src = 0; src < nranks; ++src)
+                            report_first_wrong(static_cast<char*>(ranks[r].recv[last_set]) + src * count * esz, count, config.dtype,
+                                               config.redop, config.uniform_data, kSeed, nranks, src, 0, eps, r);
+                    } else {
+                        const std::uint64_t first = coll == Collective::ReduceScatter ? (std::uint64_t)r * count : 0;
+                        report_first_wrong(ranks[r].recv[last_set], count, config.dtype, config.redop, config.uniform_data, kSeed,
+                                           nranks, -1, first, eps, r);
+                    }
+                }
                 wrong_total += host[0];
                 const unsigned int m = static_cast<unsigned int>(host[1] & 0xffffffffull);
                 float mf;
