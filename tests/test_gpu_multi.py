@@ -84,3 +84,22 @@ def test_departed_rank_is_detected_by_bounded_wait():
     for rc, out in outs:
         assert rc == 0 and "WORKER OK" in out, out
     assert any("timed out" in out for _, out in outs)
+
+
+@pytest.mark.skipif(ngpus() < 2, reason="needs two GPUs")
+def test_torch_distributed_backend_and_ddp():
+    # dist.init_process_group("b200ccl") with the real engine: collectives of every kind on CUDA tensors,
+    # a misaligned view, and torch's DistributedDataParallel, one process per GPU.
+    world = 2
+    port = free_port()
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "pg_worker.py"), "gpu", str(r), str(world), str(port)],
+                              env=dict(os.environ, PYTHONPATH=ROOT, B200CCL_WAIT_TIMEOUT_MS="5000"), stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+            out += "\n[killed after timeout]"
+        assert p.returncode == 0 and "pg worker ok" in out, out
