@@ -34,6 +34,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--matmul-n", type=int, default=8192)
     ap.add_argument("--matmuls", type=int, default=12)
+    ap.add_argument("--max-ctas", type=int, default=0,
+                    help="CTAs a collective may occupy per GPU (0: defaults); small values leave SMs to the matmuls")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -50,7 +52,7 @@ def main():
             s = socket.socket(); s.bind(("127.0.0.1", 0)); port[0] = s.getsockname()[1]; s.close()
         if world > 1:
             dist.broadcast_object_list(port, src=0)
-        comm = nn.Communicator(devices=[local], rank=rank, world_size=world, port=port[0])
+        comm = nn.Communicator(devices=[local], rank=rank, world_size=world, port=port[0], max_ctas=args.max_ctas)
         backend = CclBackend(comm)
     else:
         backend = TorchDistBackend()

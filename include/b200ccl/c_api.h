@@ -38,6 +38,7 @@ typedef struct b2_config {
     int loopback;           /* 1 = emulate loopback_ranks ranks on devices[0] */
     int loopback_ranks;
     int enable_nvls;
+    int max_ctas;           /* 0 = default; CTAs one collective may occupy per GPU */
 } b2_config;
 void b2_config_default(b2_config* cfg);
 

@@ -37,6 +37,9 @@ struct CommunicatorConfig {
     bool loopback = false;  // emulate `loopback_ranks` ranks on devices[0] with one launch per call
     int loopback_ranks = 0;
     bool enable_nvls = true;  // use NVSwitch multicast where the driver exposes it
+    // Upper bound on the CTAs one collective occupies per GPU (0 → measured defaults / B200CCL_MAX_CTAS).
+    // A small value (16-32) leaves SMs to kernels that run beside the collective, at some bandwidth cost.
+    int max_ctas = 0;
 };
 
 struct CollectiveArgs {

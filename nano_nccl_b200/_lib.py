@@ -19,6 +19,7 @@ class B2Config(ctypes.Structure):
         ("loopback", ctypes.c_int),
         ("loopback_ranks", ctypes.c_int),
         ("enable_nvls", ctypes.c_int),
+        ("max_ctas", ctypes.c_int),
     ]
 
 

@@ -38,7 +38,7 @@ class Communicator:
 
     def __init__(self, devices=None, rank=None, world_size=None, addr="127.0.0.1", port=None,
                  transport="auto", algo="auto", loopback_ranks=0, wait_timeout_ms=0.0,
-                 staging_bytes=0, enable_nvls=True, channels=0):
+                 staging_bytes=0, enable_nvls=True, channels=0, max_ctas=0):
         lib = _lib.load()
         self._lib = lib
         self._handle = ctypes.c_void_p()
@@ -59,6 +59,7 @@ class Communicator:
         cfg.staging_bytes = int(staging_bytes)
         cfg.enable_nvls = 1 if enable_nvls else 0
         cfg.channels = int(channels)
+        cfg.max_ctas = int(max_ctas)
         if devices is None:
             devices = [torch.cuda.current_device()]
         self.devices = list(devices)

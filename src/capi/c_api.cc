@@ -61,6 +61,7 @@ CommunicatorConfig to_config(const int* devices, int ndev, const b2_config* c) {
         cfg.loopback = c->loopback != 0;
         cfg.loopback_ranks = c->loopback_ranks;
         cfg.enable_nvls = c->enable_nvls != 0;
+        cfg.max_ctas = c->max_ctas;
     }
     return cfg;
 }
@@ -201,6 +202,7 @@ int b2_make_plan(int collective, int dtype, int redop, int nranks, size_t count,
         s.in_place = flags & 32u;
         s.ring_only = flags & 64u;
         s.word_aligned = flags & 128u;
+        s.max_ctas = 0;  // the tuning decides
         const sched::Plan p = sched::make_plan(s, static_cast<Algo>(forced_algo), sched::tuning_from_env());
         if (!p.error.empty()) throw std::invalid_argument(p.error);
         out[0] = static_cast<int>(p.algo);

@@ -165,6 +165,9 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
                                     : static_cast<int>(env::get_int("B200CCL_NCHANNELS", kDefaultChannels, "NANO_NCCL_NCHANNELS"));
     channels_ = std::max(1, std::min(channels_, kMaxChannels));
     tuning_ = sched::tuning_from_env();
+    if (config.max_ctas > 0) {  // an explicit cap applies to every algorithm
+        tuning_.max_ctas = tuning_.nvls_max_ctas = tuning_.twoshot_max_ctas = std::min(config.max_ctas, dev::kMaxCtas);
+    }
 
     // Rank layout: ranks are contiguous per process, in bootstrap order
     // (MPI_Allgather + MPI_Exscan in mpi_communicator.cc:134-155).

@@ -48,6 +48,7 @@ void validate_config(const CommunicatorConfig& config, int visible_devices) {
             throw std::invalid_argument("communicator supports at most " + std::to_string(kMaxRanks) +
                                         " ranks per process");
     }
+    if (config.max_ctas < 0) throw std::invalid_argument("max_ctas must not be negative");
     std::set<int> seen;
     for (int d : config.devices) {
         if (d < 0 || d >= visible_devices)

@@ -47,6 +47,10 @@ int main() {
     t_expect_throw([&] { validate_config(cfg, 4); }, "twice", "duplicate");
     cfg.devices = {0, 1, 2};
     validate_config(cfg, 4);
+    cfg.max_ctas = -1;
+    t_expect_throw([&] { validate_config(cfg, 4); }, "max_ctas", "negative CTA cap");
+    cfg.max_ctas = 16;
+    validate_config(cfg, 4);
     cfg.transport = TransportKind::Mixed;
     t_expect_throw([&] { validate_config(cfg, 4); }, "mixed", "mixed cannot be requested");
     cfg = CommunicatorConfig{};

@@ -99,3 +99,19 @@ def test_no_gpu_is_a_loud_error(lib):
     handle = ctypes.c_void_p()
     rc = lib.b2_comm_create(devs, 1, ctypes.byref(cfg), ctypes.byref(handle))
     assert rc != 0 and b"CUDA" in lib.b2_last_error()
+
+
+def test_cta_cap_from_the_environment(lib, monkeypatch):
+    WIDE, RD, WR, IMC, OMC = 1, 2, 4, 8, 16
+    monkeypatch.delenv("B200CCL_MAX_CTAS", raising=False)
+    rc, p = _plan(lib, 0, 1 << 24, WIDE | RD | WR | IMC | OMC)
+    assert rc == 0 and p[0] == 3 and p[1] == 64  # measured default for the multimem kernel
+    rc, p = _plan(lib, 0, 1 << 24, WIDE | RD | WR)
+    assert rc == 0 and p[0] == 2 and p[1] == 128  # and for two-shot
+    monkeypatch.setenv("B200CCL_MAX_CTAS", "16")  # leave SMs to kernels that run beside the collective
+    for flags in (WIDE | RD | WR | IMC | OMC, WIDE | RD | WR):
+        rc, p = _plan(lib, 0, 1 << 24, flags)
+        assert rc == 0 and p[1] == 16
+    cfg = _lib.B2Config()
+    lib.b2_config_default(ctypes.byref(cfg))
+    assert cfg.max_ctas == 0 and cfg.enable_nvls == 1
