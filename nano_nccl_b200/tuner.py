@@ -35,6 +35,7 @@ def parse_args():
                     help="comma list of oneshot,twoshot,nvls,ring,ll (ll: all_reduce up to 32 KiB, one CTA count)")
     ap.add_argument("--ctas", default="16,32,64,128")
     ap.add_argument("--graph", action="store_true", help="replay each batch from a CUDA graph")
+    ap.add_argument("--emit-tuning", default="", help="also write the crossovers as a tuning file (B200CCL_TUNING_FILE)")
     ap.add_argument("--buffers", default="symmetric", choices=["symmetric", "plain"])
     ap.add_argument("--impl", default="ours", choices=["ours", "nccl"],
                     help="nccl: time torch.distributed's NCCL collectives on the same sizes (comparator)")
@@ -187,6 +188,10 @@ def main():
             os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
             with open(args.out, "w") as f:
                 json.dump(result, f, indent=1)
+        if args.emit_tuning and args.collective == "all_reduce":
+            from .tuning_file import derive_tuning, format_tuning
+            with open(args.emit_tuning, "w") as f:
+                f.write(format_tuning(derive_tuning([result]), f"{world} GPUs, {args.dtype} {args.op}, graph={args.graph}"))
         print(f"# best per size ({world} GPUs, {args.collective}, {args.dtype} {args.op}, graph={args.graph})")
         for k in sorted(best):
             b = best[k]

@@ -3,6 +3,10 @@
 #include "core/env.h"
 
 #include <algorithm>
+#include <cstdlib>
+#include <fstream>
+#include <sstream>
+#include <stdexcept>
 
 namespace b200ccl::sched {
 
@@ -35,8 +39,62 @@ Tuning default_tuning() {
     return t;
 }
 
+Tuning tuning_from_text(const std::string& text, const Tuning& base, const std::string& origin) {
+    Tuning t = base;
+    std::istringstream in(text);
+    std::string line;
+    int lineno = 0;
+    auto trim = [](std::string s) {
+        const auto b = s.find_first_not_of(" \t\r");
+        if (b == std::string::npos) return std::string();
+        return s.substr(b, s.find_last_not_of(" \t\r") - b + 1);
+    };
+    while (std::getline(in, line)) {
+        ++lineno;
+        const auto hash = line.find('#');
+        if (hash != std::string::npos) line.erase(hash);
+        line = trim(line);
+        if (line.empty()) continue;
+        const std::string where = origin + ":" + std::to_string(lineno) + ": ";
+        const auto eq = line.find('=');
+        if (eq == std::string::npos) throw std::invalid_argument(where + "expected 'key = value'");
+        const std::string key = trim(line.substr(0, eq)), value = trim(line.substr(eq + 1));
+        std::size_t bytes = 0;
+        if (!env::parse_bytes(value, &bytes)) throw std::invalid_argument(where + "bad value '" + value + "' for " + key);
+        const int as_int = static_cast<int>(std::min<std::size_t>(bytes, 1u << 20));
+        if (key == "oneshot_max_bytes") {
+            for (int n = 2; n <= kMaxRanks; ++n) t.oneshot_max_bytes[n] = bytes;
+        } else if (key.rfind("oneshot_max_bytes.", 0) == 0) {
+            const std::string nstr = key.substr(18);
+            char* end = nullptr;
+            const long n = std::strtol(nstr.c_str(), &end, 10);
+            if (nstr.empty() || *end != '\0' || n < 2 || n > kMaxRanks)
+                throw std::invalid_argument(where + "rank count in '" + key + "' must be 2.." + std::to_string(kMaxRanks));
+            t.oneshot_max_bytes[n] = bytes;
+        } else if (key == "nvls_min_bytes") t.nvls_min_bytes = bytes;
+        else if (key == "max_ctas") t.max_ctas = std::max(as_int, 1);
+        else if (key == "nvls_max_ctas") t.nvls_max_ctas = std::max(as_int, 1);
+        else if (key == "twoshot_max_ctas") t.twoshot_max_ctas = std::max(as_int, 1);
+        else if (key == "nvls_unroll") t.nvls_unroll = as_int;
+        else if (key == "bytes_per_cta") t.bytes_per_cta = std::max<std::size_t>(bytes, 1);
+        else if (key == "oneshot_bytes_per_cta") t.oneshot_bytes_per_cta = std::max<std::size_t>(bytes, 1);
+        else if (key == "ll_max_bytes") t.ll_max_bytes = std::min(bytes, kLlPlanMaxBytes);
+        else throw std::invalid_argument(where + "unknown key '" + key + "'");
+    }
+    return t;
+}
+
+Tuning tuning_from_file(const std::string& path, const Tuning& base) {
+    std::ifstream f(path);
+    if (!f) throw std::invalid_argument("tuning file '" + path + "' cannot be read");
+    std::stringstream text;
+    text << f.rdbuf();
+    return tuning_from_text(text.str(), base, path);
+}
+
 Tuning tuning_from_env() {
     Tuning t = default_tuning();
+    if (const char* path = env::get("B200CCL_TUNING_FILE")) t = tuning_from_file(path, t);
     if (env::get("B200CCL_ONESHOT_MAX_BYTES")) {
         const std::size_t v = env::get_bytes("B200CCL_ONESHOT_MAX_BYTES", 0);
         for (int n = 0; n <= kMaxRanks; ++n) t.oneshot_max_bytes[n] = v;

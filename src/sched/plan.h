@@ -56,7 +56,15 @@ struct Tuning {
     std::size_t ll_max_bytes = 0;
 };
 Tuning default_tuning();
+// default_tuning(), then the file named by B200CCL_TUNING_FILE (if set), then the B200CCL_* variables.
 Tuning tuning_from_env();
+// Applies a tuning file to `base`. One `key = value` per line, `#` starts a comment; byte counts take
+// K/M/G suffixes. Keys: oneshot_max_bytes (all rank counts) or oneshot_max_bytes.<nranks>, nvls_min_bytes,
+// max_ctas, nvls_max_ctas, twoshot_max_ctas, nvls_unroll, bytes_per_cta, oneshot_bytes_per_cta, ll_max_bytes.
+// `python -m nano_nccl_b200.tuner --emit-tuning FILE` writes such a file from its measurements.
+// Throws std::invalid_argument naming the file and line on an unknown key or a bad value.
+Tuning tuning_from_text(const std::string& text, const Tuning& base, const std::string& origin);
+Tuning tuning_from_file(const std::string& path, const Tuning& base);
 
 Plan make_plan(const CallShape& shape, Algo forced, const Tuning& tuning);
 

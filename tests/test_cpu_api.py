@@ -115,3 +115,60 @@ def test_cta_cap_from_the_environment(lib, monkeypatch):
     cfg = _lib.B2Config()
     lib.b2_config_default(ctypes.byref(cfg))
     assert cfg.max_ctas == 0 and cfg.enable_nvls == 1
+
+
+def test_tuning_file(lib, monkeypatch, tmp_path):
+    WIDE, RD, WR, IMC, OMC, WORD = 1, 2, 4, 8, 16, 128
+    path = tmp_path / "b200.tuning"
+    path.write_text("# measured on some machine\noneshot_max_bytes.8 = 64K   # eight ranks\nnvls_min_bytes = 1M\n"
+                    "nvls_max_ctas = 48\nll_max_bytes = 4K\n\n")
+    monkeypatch.setenv("B200CCL_TUNING_FILE", str(path))
+    for var in ("B200CCL_MAX_CTAS", "B200CCL_LL_MAX_BYTES", "B200CCL_NVLS_MIN_BYTES", "B200CCL_ONESHOT_MAX_BYTES"):
+        monkeypatch.delenv(var, raising=False)
+    rc, p = _plan(lib, 0, 8192, WIDE | RD | WR | IMC | OMC)          # 32 KiB: one-shot now (default: multimem)
+    assert rc == 0 and p[0] == 1
+    rc, p = _plan(lib, 0, 8192, WIDE | RD | WR | IMC | OMC, nranks=4)  # other rank counts keep their default
+    assert rc == 0 and p[0] == 2                                      # (8 KiB one-shot limit there, multimem from 1 MiB)
+    rc, p = _plan(lib, 0, 1 << 24, WIDE | RD | WR | IMC | OMC)
+    assert rc == 0 and p[0] == 3 and p[1] == 48
+    rc, p = _plan(lib, 0, 512, WIDE | RD | WR | WORD)
+    assert rc == 0 and p[0] == 5                                      # low-latency kernel switched on by the file
+    monkeypatch.setenv("B200CCL_LL_MAX_BYTES", "0")                   # the environment still has the last word
+    rc, p = _plan(lib, 0, 512, WIDE | RD | WR | WORD)
+    assert rc == 0 and p[0] == 1
+    path.write_text("nvls_min_bytes = 1M\nwarp_speed = 9\n")
+    rc, p = _plan(lib, 0, 512, WIDE | RD | WR)
+    assert rc == 2 and b"b200.tuning:2: unknown key 'warp_speed'" in lib.b2_last_error()
+    path.write_text("oneshot_max_bytes.9 = 1K\n")
+    rc, p = _plan(lib, 0, 512, WIDE | RD | WR)
+    assert rc == 2 and b"must be 2..8" in lib.b2_last_error()
+    monkeypatch.setenv("B200CCL_TUNING_FILE", str(tmp_path / "missing"))
+    rc, p = _plan(lib, 0, 512, WIDE | RD | WR)
+    assert rc == 2 and b"cannot be read" in lib.b2_last_error()
+
+
+def test_tuning_file_from_tuner_tables():
+    import json
+    import os
+    from nano_nccl_b200.tuning_file import derive_tuning, format_tuning
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    tables = [json.load(open(os.path.join(root, "tuning", f"b200_n{n}_all_reduce_graph.json"))) for n in (8, 4)]
+    values = derive_tuning(tables)
+    assert values["oneshot_max_bytes.8"] == 8192 and values["oneshot_max_bytes.4"] == 8192  # what default_tuning() encodes
+    assert 16 << 10 <= values["nvls_min_bytes"] <= 256 << 10
+    # a synthetic table: ll wins up to 2 KiB, one-shot up to 8 KiB, two-shot in between, multimem from 1 MiB; 48 CTAs best
+    rows = []
+    for size in (1024, 2048, 4096, 8192, 65536, 1 << 20, 64 << 20):
+        t = {"ll": 5 if size <= 2048 else 50, "oneshot": 8 if size <= 8192 else 80 + size / 1e4,
+             "twoshot": 10 + size / 1e5, "nvls": 12 + size / 2e5 if size >= 1 << 20 else 14 + size / 1e5}
+        for algo, us in t.items():
+            if algo == "ll" and size > 32768:
+                continue
+            for ctas in (48, 64):
+                rows.append({"collective": "all_reduce", "algo": algo, "requested": algo, "max_ctas": ctas, "bytes": size,
+                             "time_us": us * (1.0 if ctas == 48 else 1.1)})
+    values = derive_tuning([{"n_gpus": 8, "rows": rows}])
+    assert values == {"oneshot_max_bytes.8": 8192, "ll_max_bytes": 2048, "nvls_min_bytes": 1 << 20, "nvls_max_ctas": 48,
+                      "twoshot_max_ctas": 48}
+    text = format_tuning(values, "synthetic")
+    assert "ll_max_bytes = 2048\n" in text and text.startswith("# b200ccl tuning file")
