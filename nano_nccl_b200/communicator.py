@@ -238,6 +238,13 @@ class Communicator:
             self._lib.b2_bootstrap_destroy(self._bootstrap)
             self._bootstrap = ctypes.c_void_p()
 
+    def __enter__(self):
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        self.close()
+        return False
+
     def __del__(self):
         try:
             self.close()
