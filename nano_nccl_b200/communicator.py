@@ -160,17 +160,35 @@ class Communicator:
         _lib.check(self._lib.b2_comm_unregister(self._handle, ptrs))
 
     # -- collectives -----------------------------------------------------------------------------
-    def _run(self, coll, outs, inps, op, streams, count, in_place=False):
+    def _device_index(self, i):
+        return self.devices[0] if len(self.devices) == 1 else self.devices[i]
+
+    def _check_tensor(self, what, i, t, dtype, numel):
+        """Everything the C layer cannot see behind a raw pointer: a tensor that is too small, of
+        another dtype or on another GPU would make the kernel write outside the allocation."""
+        if not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"{what}[{i}] must be a contiguous CUDA tensor")
+        if t.dtype != dtype:
+            raise ValueError(f"{what}[{i}] has dtype {t.dtype}, expected {dtype}")
+        if t.numel() != numel:
+            raise ValueError(f"{what}[{i}] has {t.numel()} elements, expected {numel}")
+        want = self._device_index(i)
+        if t.device.index != want:
+            raise ValueError(f"{what}[{i}] lives on cuda:{t.device.index}, local rank {i} of this communicator drives cuda:{want}")
+
+    def _run(self, coll, outs, inps, op, streams, count, in_numel, out_numel, in_place=False):
+        if op not in _OPS:
+            raise ValueError(f"unknown reduction '{op}'")
         if isinstance(inps, torch.Tensor):
             # Fast path: one local rank, one tensor each way.
-            if self.local_ranks != 1:
+            if self.local_ranks != 1 or not isinstance(outs, torch.Tensor):
                 raise ValueError(f"need one tensor per local rank ({self.local_ranks})")
             dtype = inps.dtype
             code = _DTYPES.get(dtype)
             if code is None:
                 raise ValueError(f"unsupported dtype {dtype}")
-            if not (inps.is_cuda and outs.is_cuda and inps.is_contiguous() and outs.is_contiguous() and outs.dtype == dtype):
-                raise ValueError("tensors must be contiguous CUDA tensors of one dtype")
+            self._check_tensor("input", 0, inps, dtype, in_numel)
+            self._check_tensor("output", 0, outs, dtype, out_numel)
             if streams is None:
                 sp = torch.cuda.current_stream(inps.device).cuda_stream
             else:
@@ -182,18 +200,20 @@ class Communicator:
             if rc != 0:
                 _lib.check(rc)
             return
-        if len(inps) != self.local_ranks or len(outs) != self.local_ranks:
+        if isinstance(outs, torch.Tensor) or len(inps) != self.local_ranks or len(outs) != self.local_ranks:
             raise ValueError(f"need one tensor per local rank ({self.local_ranks})")
         dtype = inps[0].dtype
         if dtype not in _DTYPES:
             raise ValueError(f"unsupported dtype {dtype}")
-        for t in list(inps) + list(outs):
-            if not t.is_cuda or not t.is_contiguous() or t.dtype != dtype:
-                raise ValueError("tensors must be contiguous CUDA tensors of one dtype")
+        for i, (x, y) in enumerate(zip(inps, outs)):
+            self._check_tensor("input", i, x, dtype, in_numel)
+            self._check_tensor("output", i, y, dtype, out_numel)
         if streams is None:
             streams = [torch.cuda.current_stream(t.device).cuda_stream for t in inps]
         elif not isinstance(streams, (list, tuple)):
             streams = [streams] * len(inps)
+        if len(streams) != self.local_ranks:
+            raise ValueError(f"need one stream per local rank ({self.local_ranks})")
         streams = [s.cuda_stream if hasattr(s, "cuda_stream") else int(s) for s in streams]
         n = self.local_ranks
         send = (ctypes.c_void_p * n)(*[t.data_ptr() for t in inps])
@@ -209,7 +229,8 @@ class Communicator:
         first_in = inp if isinstance(inp, torch.Tensor) else inp[0]
         first_out = out if isinstance(out, torch.Tensor) else out[0]
         in_place = first_in.data_ptr() == first_out.data_ptr()
-        self._run("all_reduce", out, inp, op, stream, first_in.numel(), in_place)
+        n = first_in.numel()
+        self._run("all_reduce", out, inp, op, stream, n, n, n, in_place)
         return out
 
     def reduce_scatter(self, out, inp, op="sum", stream=None):
@@ -218,7 +239,8 @@ class Communicator:
         first_in = inp if isinstance(inp, torch.Tensor) else inp[0]
         if first_in.numel() != first_out.numel() * self.world_size:
             raise ValueError("reduce_scatter: input must hold world_size blocks of the output's size")
-        self._run("reduce_scatter", out, inp, op, stream, first_out.numel())
+        n = first_out.numel()
+        self._run("reduce_scatter", out, inp, op, stream, n, n * self.world_size, n)
         return out
 
     def all_gather(self, out, inp, stream=None):
@@ -227,8 +249,22 @@ class Communicator:
         first_in = inp if isinstance(inp, torch.Tensor) else inp[0]
         if first_out.numel() != first_in.numel() * self.world_size:
             raise ValueError("all_gather: output must hold world_size blocks of the input's size")
-        self._run("all_gather", out, inp, "sum", stream, first_in.numel())
+        n = first_in.numel()
+        self._run("all_gather", out, inp, "sum", stream, n, n, n * self.world_size)
         return out
+
+    def free(self, tensors):
+        """Releases the symmetric allocation behind tensor(s) returned by ``empty()``. COLLECTIVE: every
+        process calls it for the same allocation, in the same order. The tensors (and every view of
+        them) must not be used afterwards: their memory is unmapped."""
+        if isinstance(tensors, torch.Tensor):
+            tensors = [tensors]
+        if len(tensors) != self.local_ranks:
+            raise ValueError(f"need one tensor per local rank ({self.local_ranks})")
+        ptrs = (ctypes.c_void_p * self.local_ranks)(*[t.data_ptr() for t in tensors])
+        _lib.check(self._lib.b2_comm_free_symmetric(self._handle, ptrs))
+        gone = {int(p) for p in ptrs}
+        self._blocks = [b for b in self._blocks if int(b.ptr) not in gone]
 
     def close(self):
         if self._handle:

@@ -81,12 +81,15 @@ private:
     Located locate(const void* p, std::size_t bytes, int grank) const;
     void wait_previous(Local& l, cudaStream_t stream);
     void record_done(Local& l, cudaStream_t stream);
+    // in_loc / out_loc: where each local rank's buffer lies; null when the buffers of this call do
+    // not sit at one common offset of one window (then the window's peer addresses say nothing
+    // about the other ranks' buffers and must not be used).
     void launch_all_reduce(const CollectiveArgs& args, const sched::Plan& plan, bool wide,
-                           const std::vector<Located>& in_loc, const std::vector<Located>& out_loc);
+                           const std::vector<Located>* in_loc, const std::vector<Located>* out_loc);
     void launch_reduce_scatter(const CollectiveArgs& args, const sched::Plan& plan, bool wide,
-                               const std::vector<Located>& in_loc);
+                               const std::vector<Located>* in_loc);
     void launch_all_gather(const CollectiveArgs& args, const sched::Plan& plan, bool wide,
-                           const std::vector<Located>& in_loc, const std::vector<Located>& out_loc);
+                           const std::vector<Located>* in_loc, const std::vector<Located>* out_loc);
     void fill_common(dev::CollArgs& a, const Local& l) const;
     void launch_reduce_ranks(const CollectiveArgs& args, std::vector<dev::CollArgs>& per_rank, bool wide,
                              bool nvls, int grid);
@@ -603,9 +606,9 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
     }
     if (plan.stage_in || plan.stage_out) ensure_staging();
     switch (collective) {
-        case Collective::AllReduce: launch_all_reduce(args, plan, wide, in_loc, out_loc); break;
-        case Collective::ReduceScatter: launch_reduce_scatter(args, plan, wide, in_loc); break;
-        case Collective::AllGather: launch_all_gather(args, plan, wide, in_loc, out_loc); break;
+        case Collective::AllReduce: launch_all_reduce(args, plan, wide, in_sym ? &in_loc : nullptr, out_sym ? &out_loc : nullptr); break;
+        case Collective::ReduceScatter: launch_reduce_scatter(args, plan, wide, in_sym ? &in_loc : nullptr); break;
+        case Collective::AllGather: launch_all_gather(args, plan, wide, in_sym ? &in_loc : nullptr, out_sym ? &out_loc : nullptr); break;
     }
 }
 
@@ -655,7 +658,7 @@ void Communicator::Impl::launch_low_latency(const CollectiveArgs& args) {
 }
 
 void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sched::Plan& plan, bool wide,
-                                           const std::vector<Located>& in_loc, const std::vector<Located>& out_loc) {
+                                           const std::vector<Located>* in_win, const std::vector<Located>* out_win) {
     const std::size_t esz = dtype_size(args.dtype);
     const std::size_t pack = wide ? 16 : esz;
     const std::size_t total_packs = args.count * esz / pack;
@@ -679,14 +682,14 @@ void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sch
             for (int p = 0; p < nranks_; ++p) {
                 // input table
                 if (plan.stage_in) a.in[p] = stage_->rank_ptr(p);
-                else if (in_loc[i].region >= 0)
-                    a.in[p] = static_cast<const char*>(windows_[in_loc[i].region].ptr[p]) + in_loc[i].offset + off;
+                else if (in_win != nullptr)
+                    a.in[p] = static_cast<const char*>(windows_[(*in_win)[i].region].ptr[p]) + (*in_win)[i].offset + off;
                 else if (direct) a.in[p] = static_cast<const char*>(args.send_buffers[p]) + off;
                 // output table
                 if (plan.stage_out) a.out[p] = static_cast<char*>(stage_->rank_ptr(p)) + staging_half_;
                 else if (oneshot) a.out[p] = nullptr;
-                else if (out_loc[i].region >= 0)
-                    a.out[p] = static_cast<char*>(windows_[out_loc[i].region].ptr[p]) + out_loc[i].offset + off;
+                else if (out_win != nullptr)
+                    a.out[p] = static_cast<char*>(windows_[(*out_win)[i].region].ptr[p]) + (*out_win)[i].offset + off;
                 else if (direct) a.out[p] = static_cast<char*>(args.recv_buffers[p]) + off;
             }
             if (oneshot) a.out[local_[i].grank] = static_cast<char*>(args.recv_buffers[i]) + off;
@@ -694,9 +697,9 @@ void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sch
             if (plan.stage_out) a.user_out = static_cast<char*>(args.recv_buffers[i]) + off;
             if (nvls) {
                 a.mc_in = plan.stage_in ? static_cast<const char*>(stage_->multicast_ptr())
-                                        : static_cast<const char*>(windows_[in_loc[i].region].mc) + in_loc[i].offset + off;
+                                        : static_cast<const char*>(windows_[(*in_win)[i].region].mc) + (*in_win)[i].offset + off;
                 a.mc_out = plan.stage_out ? static_cast<char*>(stage_->multicast_ptr()) + staging_half_
-                                          : static_cast<char*>(windows_[out_loc[i].region].mc) + out_loc[i].offset + off;
+                                          : static_cast<char*>(windows_[(*out_win)[i].region].mc) + (*out_win)[i].offset + off;
             }
         }
         launch_reduce_ranks(args, per, wide, nvls, plan.grid);
@@ -704,7 +707,7 @@ void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sch
 }
 
 void Communicator::Impl::launch_reduce_scatter(const CollectiveArgs& args, const sched::Plan& plan, bool wide,
-                                               const std::vector<Located>& in_loc) {
+                                               const std::vector<Located>* in_win) {
     const std::size_t esz = dtype_size(args.dtype);
     const std::size_t pack = wide ? 16 : esz;
     const std::size_t block_packs = args.count * esz / pack;  // one rank's block
@@ -727,20 +730,20 @@ void Communicator::Impl::launch_reduce_scatter(const CollectiveArgs& args, const
             if (args.redop == RedOp::Avg) a.scale = 1.0f / static_cast<float>(nranks_);
             for (int p = 0; p < nranks_; ++p) {
                 if (plan.stage_in) a.in[p] = stage_->rank_ptr(p);
-                else if (in_loc[i].region >= 0)
-                    a.in[p] = static_cast<const char*>(windows_[in_loc[i].region].ptr[p]) + in_loc[i].offset + off;
+                else if (in_win != nullptr)
+                    a.in[p] = static_cast<const char*>(windows_[(*in_win)[i].region].ptr[p]) + (*in_win)[i].offset + off;
                 else if (direct) a.in[p] = static_cast<const char*>(args.send_buffers[p]) + off;
             }
             a.out[local_[i].grank] = static_cast<char*>(args.recv_buffers[i]) + off;
             if (plan.stage_in) a.user_in = static_cast<const char*>(args.send_buffers[i]) + off;
-            if (nvls) a.mc_in = static_cast<const char*>(windows_[in_loc[i].region].mc) + in_loc[i].offset + off;
+            if (nvls) a.mc_in = static_cast<const char*>(windows_[(*in_win)[i].region].mc) + (*in_win)[i].offset + off;
         }
         launch_reduce_ranks(args, per, wide, nvls, plan.grid);
     }
 }
 
 void Communicator::Impl::launch_all_gather(const CollectiveArgs& args, const sched::Plan& plan, bool wide,
-                                           const std::vector<Located>& in_loc, const std::vector<Located>& out_loc) {
+                                           const std::vector<Located>* in_win, const std::vector<Located>* out_win) {
     const std::size_t esz = dtype_size(args.dtype);
     const std::size_t bytes = args.count * esz;
     std::size_t pack = wide ? 16 : (bytes % 4 == 0 ? 4 : 2);
@@ -773,12 +776,12 @@ void Communicator::Impl::launch_all_gather(const CollectiveArgs& args, const sch
             for (int p = 0; p < nranks_; ++p) {
                 if (plan.gather_mode == 1) {  // pull: need everyone's input
                     if (plan.stage_in) a.in[p] = stage_->rank_ptr(p);
-                    else if (in_loc[i].region >= 0)
-                        a.in[p] = static_cast<const char*>(windows_[in_loc[i].region].ptr[p]) + in_loc[i].offset + off;
+                    else if (in_win != nullptr)
+                        a.in[p] = static_cast<const char*>(windows_[(*in_win)[i].region].ptr[p]) + (*in_win)[i].offset + off;
                     else if (direct) a.in[p] = static_cast<const char*>(args.send_buffers[p]) + off;
                 } else if (plan.gather_mode == 0) {  // push: need everyone's output
-                    if (out_loc[i].region >= 0)
-                        a.out[p] = static_cast<char*>(windows_[out_loc[i].region].ptr[p]) + out_loc[i].offset + off;
+                    if (out_win != nullptr)
+                        a.out[p] = static_cast<char*>(windows_[(*out_win)[i].region].ptr[p]) + (*out_win)[i].offset + off;
                     else if (direct) a.out[p] = static_cast<char*>(args.recv_buffers[p]) + off;
                 }
             }
@@ -786,7 +789,7 @@ void Communicator::Impl::launch_all_gather(const CollectiveArgs& args, const sch
             if (plan.gather_mode != 0) a.out[local_[i].grank] = static_cast<char*>(args.recv_buffers[i]) + off;
             if (plan.stage_in) a.user_in = static_cast<const char*>(args.send_buffers[i]) + off;
             if (plan.gather_mode == 2)
-                a.mc_out = static_cast<char*>(windows_[out_loc[i].region].mc) + out_loc[i].offset + off;
+                a.mc_out = static_cast<char*>(windows_[(*out_win)[i].region].mc) + (*out_win)[i].offset + off;
         }
         launch_gather_ranks(args, per, plan.grid);
     }

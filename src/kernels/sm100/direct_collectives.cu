@@ -426,10 +426,28 @@ extern "C" int b2_local_all_reduce_no_alloc(const void* const* inputs, void* con
     if (dtype < 0 || dtype > 2) return reject("unsupported dtype");
     if (redop < 0 || redop > 3) return reject("unknown reduction operator");
     if (inputs == nullptr || outputs == nullptr) return reject("inputs and outputs must be non-null");
+    const std::size_t elem_bytes = dtype_size(static_cast<DType>(dtype));
+    if (count > SIZE_MAX / elem_bytes) return reject("count * element size does not fit in size_t");
+    const std::size_t span = count * elem_bytes;
+    // Byte ranges [ptr, ptr + span) of two buffers share at least one byte.
+    auto overlap = [span](const void* a, const void* b) {
+        const std::uintptr_t x = reinterpret_cast<std::uintptr_t>(a), y = reinterpret_cast<std::uintptr_t>(b);
+        return x < y ? y - x < span : x - y < span;
+    };
     for (int r = 0; r < nranks; ++r) {
         if (inputs[r] == nullptr || outputs[r] == nullptr) return reject("every buffer must be non-null");
-        for (int q = 0; q < nranks; ++q)
+        if (reinterpret_cast<std::uintptr_t>(inputs[r]) > UINTPTR_MAX - span ||
+            reinterpret_cast<std::uintptr_t>(outputs[r]) > UINTPTR_MAX - span)
+            return reject("a buffer's byte range wraps around the address space");
+    }
+    for (int r = 0; r < nranks; ++r) {
+        for (int q = 0; q < nranks; ++q) {
             if (inputs[r] == outputs[q]) return reject("in-place operation is not supported");
+            if (overlap(inputs[r], outputs[q]))
+                return reject("input " + std::to_string(r) + " and output " + std::to_string(q) + " overlap");
+            if (q > r && overlap(outputs[r], outputs[q]))
+                return reject("outputs " + std::to_string(r) + " and " + std::to_string(q) + " overlap");
+        }
     }
     void* scratch = nullptr;
     cudaError_t st = no_alloc_scratch_address(&scratch);

@@ -20,7 +20,9 @@
  * What it computes. `nranks` input buffers and `nranks` output buffers of `count` elements, all on
  * the current device. Every output receives the element-wise reduction (sum, avg, max, min; fp32
  * accumulation for fp16/bf16; NaN-propagating max/min) of all inputs. Inputs and outputs must not
- * overlap. Work is enqueued on `stream`; the call returns without waiting for it.
+ * overlap: any two byte ranges that share a byte (an input with an output, or two outputs) are
+ * rejected, as is a count whose byte size overflows size_t. Work is enqueued on `stream`; the call
+ * returns without waiting for it.
  *
  * Scratch. One control block per emulated rank (barrier flags, per-CTA epochs, abort word) in a
  * file-scope `static __device__` array of B2_NO_ALLOC_MAX_RANKS blocks, about 13 KiB each, roughly

@@ -82,6 +82,14 @@ def test_rejects_what_the_fixed_array_cannot_hold():
     msg = lib.b2_last_error().decode()
     assert "nranks = 9" in msg and "1..8" in msg
     assert call(fn, x[:2], x[:2], "sum") == 2 and b"in-place" in lib.b2_last_error()
+    # ranges that overlap part-way, and two outputs that alias, would race inside the kernel
+    big = torch.zeros(64, device="cuda")
+    assert call(fn, [big[:16], big[32:48]], [big[8:24], big[48:64]], "sum") == 2 and b"overlap" in lib.b2_last_error()
+    assert call(fn, x[:2], [big[:16], big[:16]], "sum") == 2 and b"outputs 0 and 1 overlap" in lib.b2_last_error()
+    # a count whose byte size does not fit in size_t
+    ins = (ctypes.c_void_p * 1)(x[0].data_ptr())
+    outs = (ctypes.c_void_p * 1)(y[0].data_ptr())
+    assert fn(ins, outs, 1, (1 << 63), 0, 0, None, None) == 2 and b"does not fit" in lib.b2_last_error()
     # and a valid call still works afterwards
     a = [torch.ones(16, device="cuda"), torch.full((16,), 2.0, device="cuda")]
     b = [torch.empty(16, device="cuda") for _ in range(2)]
