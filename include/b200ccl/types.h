@@ -29,8 +29,11 @@ enum class Collective : int { AllReduce = 0, ReduceScatter = 1, AllGather = 2 };
 //   TwoShot  rank r reduces shard r from all peers, then stores it into every peer's output
 //   Nvls     NVSwitch multicast: multimem.ld_reduce on the own shard, multimem.st broadcast
 //   Ring     ring over per-edge Simple-protocol FIFOs (works over SHM / socket / RDMA edges)
-//   LowLatency  flag-in-data exchange without barriers for messages up to 32 KiB (AllReduce only)
-enum class Algo : int { Auto = 0, OneShot = 1, TwoShot = 2, Nvls = 3, Ring = 4, LowLatency = 5 };
+//   LowLatency  flag-in-data exchange without barriers for messages up to 128 KiB (AllReduce only)
+//   Copy     one rank only: the collective is a device-to-device copy (TMA bulk copies); reported, never requested
+//   Pipeline AllReduce of buffers that peers cannot address: copy into the staging arena, reduce and copy out
+//            run as a tile pipeline inside one kernel (TMA bulk copies for the local tiles)
+enum class Algo : int { Auto = 0, OneShot = 1, TwoShot = 2, Nvls = 3, Ring = 4, LowLatency = 5, Copy = 6, Pipeline = 7 };
 
 const char* dtype_name(DType d);
 const char* redop_name(RedOp r);

@@ -14,7 +14,7 @@ from . import _lib
 _DTYPES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 _OPS = {"sum": 0, "avg": 1, "max": 2, "min": 3}
 _COLL = {"all_reduce": 0, "reduce_scatter": 1, "all_gather": 2}
-_ALGO_NAMES = ["auto", "oneshot", "twoshot", "nvls", "ring", "ll"]
+_ALGO_NAMES = ["auto", "oneshot", "twoshot", "nvls", "ring", "ll", "copy", "pipeline"]
 
 
 class _SymmetricBlock:

@@ -32,7 +32,7 @@ def parse_args():
     ap.add_argument("--dtype", default="float", choices=["float", "fp16", "bf16"])
     ap.add_argument("--op", default="sum")
     ap.add_argument("--algos", default="oneshot,twoshot,nvls",
-                    help="comma list of oneshot,twoshot,nvls,ring,ll (ll: all_reduce up to 32 KiB, one CTA count)")
+                    help="comma list of oneshot,twoshot,nvls,ring,ll (ll: all_reduce up to 128 KiB, one CTA count)")
     ap.add_argument("--ctas", default="16,32,64,128")
     ap.add_argument("--graph", action="store_true", help="replay each batch from a CUDA graph")
     ap.add_argument("--emit-tuning", default="", help="also write the crossovers as a tuning file (B200CCL_TUNING_FILE)")
@@ -115,7 +115,7 @@ def main():
             while size <= args.max_bytes:
                 if algo == "oneshot" and size > (8 << 20):
                     break
-                if algo == "ll" and (size > (32 << 10) or args.collective != "all_reduce" or ctas != cta_list[0]):
+                if algo == "ll" and (size > (128 << 10) or args.collective != "all_reduce" or ctas != cta_list[0]):
                     break  # fixed grid of 8 CTAs: one pass is enough
                 numel = max(size // esize, 1)
                 in_mult = world if args.collective == "reduce_scatter" else 1

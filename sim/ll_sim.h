@@ -23,7 +23,7 @@ struct LlSimConfig {
     int lanes = 4;                        // "threads" per CTA: word w belongs to CTA (w / lanes) % ctas
     RedOp redop = RedOp::Sum;
     std::vector<std::size_t> call_words;  // one entry per call: message length in 4-byte words (> 0)
-    std::size_t max_words = 1024;         // slot capacity per source (device: 8192)
+    std::size_t max_words = 1024;         // slot capacity per source (device: 32768)
     double wait_timeout_ms = 2000.0;
     int slow_rank = -1;                   // this rank sleeps a little before every call (skew)
     int stall_rank = -1;                  // failure injection: this rank never starts ...

@@ -20,6 +20,7 @@
 #include "kernels/sm100/dev_types.h"
 #include "kernels/sm100/direct_collectives.h"
 #include "kernels/sm100/ll_allreduce.h"
+#include "kernels/sm100/local_copy.h"
 #include "mem/ipc_window.h"
 #include "mem/symmetric.h"
 #include "sched/plan.h"
@@ -28,6 +29,7 @@
 
 #include <algorithm>
 #include <cstring>
+#include <initializer_list>
 #include <sstream>
 #include <stdexcept>
 
@@ -41,6 +43,18 @@ struct Located {
     int region = -1;  // index into windows_, or -1
     std::size_t offset = 0;
 };
+
+// FNV-1a over the facts of a launch that every rank must share; never 0 (0 means "no check").
+unsigned long long plan_fingerprint(std::initializer_list<unsigned long long> facts) {
+    unsigned long long h = 1469598103934665603ull;
+    for (unsigned long long f : facts) {
+        for (int b = 0; b < 8; ++b) {
+            h ^= (f >> (8 * b)) & 0xffull;
+            h *= 1099511628211ull;
+        }
+    }
+    return h == 0 ? 1 : h;
+}
 
 }  // namespace
 
@@ -77,7 +91,7 @@ private:
     };
 
     void resolve_transport();
-    void ensure_staging();
+    void ensure_staging(const CollectiveArgs& args);
     Located locate(const void* p, std::size_t bytes, int grank) const;
     void wait_previous(Local& l, cudaStream_t stream);
     void record_done(Local& l, cudaStream_t stream);
@@ -91,7 +105,7 @@ private:
     void launch_all_gather(const CollectiveArgs& args, const sched::Plan& plan, bool wide,
                            const std::vector<Located>* in_loc, const std::vector<Located>* out_loc);
     void fill_common(dev::CollArgs& a, const Local& l) const;
-    void launch_reduce_ranks(const CollectiveArgs& args, std::vector<dev::CollArgs>& per_rank, bool wide,
+    void launch_reduce_ranks(const CollectiveArgs& args, std::vector<dev::CollArgs>& per_rank, int pack_bytes,
                              bool nvls, int grid);
     void launch_gather_ranks(const CollectiveArgs& args, std::vector<dev::GatherArgs>& per_rank, int grid);
     void launch_low_latency(const CollectiveArgs& args);
@@ -229,6 +243,9 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
         group_ = group;
         alloc_.reset(new mem::SymmetricAllocator(group));
         ctrl_ = alloc_->allocate(sizeof(dev::ControlBlock), "control");
+        // Allocation is collective (and clears memory, which synchronises the device), so what the
+        // small-message path needs exists before the first call rather than inside it.
+        if (nranks_ >= 2) ll_area_ = alloc_->allocate(kernels::ll_area_bytes(nranks_), "low-latency slots");
     }
 
     for (auto& l : local_) {
@@ -307,12 +324,20 @@ void Communicator::Impl::check_async_error() const {
             const volatile dev::Status* s = l.status;
             if (s && s->code != dev::kStatusOk) {
                 std::ostringstream os;
-                const char* what = s->code == dev::kStatusTimeout ? "device wait timed out"
-                                   : s->code == dev::kStatusAborted ? "device wait aborted"
-                                                                    : "device self-check failed";
-                os << what << ": rank " << l.grank << " cta " << s->cta << " waited "
-                   << static_cast<double>(s->waited_ns) * 1e-6 << " ms for rank " << s->peer << " at site " << s->where
-                   << " (epoch/step " << s->epoch << ")";
+                if (s->code == dev::kStatusPlanMismatch) {
+                    os << "ranks disagree on the plan: rank " << l.grank << " and rank " << s->peer
+                       << " launched this collective with different algorithms, grids, pack widths or staging; every rank "
+                          "must pass the same count and dtype, and buffers of the same kind (symmetric, registered or plain) "
+                          "and alignment";
+                } else if (s->code == dev::kStatusBadArgs) {
+                    os << "device self-check failed: rank " << l.grank << " cta " << s->cta << " computed index " << s->epoch
+                       << " beyond the buffer extent at site " << s->where << "; the access was skipped";
+                } else {
+                    const char* what = s->code == dev::kStatusTimeout ? "device wait timed out" : "device wait aborted";
+                    os << what << ": rank " << l.grank << " cta " << s->cta << " waited "
+                       << static_cast<double>(s->waited_ns) * 1e-6 << " ms for rank " << s->peer << " at site " << s->where
+                       << " (epoch/step " << s->epoch << ")";
+                }
                 latched_ = os.str();
                 break;
             }
@@ -325,8 +350,17 @@ void Communicator::Impl::check_async_error() const {
     if (!latched_.empty()) throw std::runtime_error(latched_);
 }
 
-void Communicator::Impl::ensure_staging() {
-    if (!stage_) stage_ = alloc_->allocate(staging_half_ * 2, "staging");
+void Communicator::Impl::ensure_staging(const CollectiveArgs& args) {
+    if (stage_) return;
+    // The arena is allocated on the first call that needs it. That allocation is collective between
+    // processes and synchronises the device, neither of which a stream capture survives.
+    for (cudaStream_t stream : args.streams) {
+        cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &st) == cudaSuccess && st == cudaStreamCaptureStatusActive)
+            throw std::runtime_error("the staging arena must be allocated outside a stream capture: run one collective on "
+                                     "buffers of this kind before capturing, or use symmetric or registered buffers");
+    }
+    stage_ = alloc_->allocate(staging_half_ * 2, "staging");
 }
 
 Located Communicator::Impl::locate(const void* p, std::size_t bytes, int grank) const {
@@ -421,27 +455,35 @@ void Communicator::Impl::fill_common(dev::CollArgs& a, const Local& l) const {
 }
 
 void Communicator::Impl::launch_reduce_ranks(const CollectiveArgs& args, std::vector<dev::CollArgs>& per_rank,
-                                             bool wide, bool nvls, int grid) {
+                                             int pack_bytes, bool nvls, int grid) {
     kernels::LaunchConfig cfg;
     cfg.grid = std::min(grid, dev::kMaxCtas);
     cfg.block = dev::kBlockThreads;
     cfg.nvls_unroll = tuning_.nvls_unroll;
+    if (loopback_) cfg.grid = std::min(cfg.grid, std::max(1, 128 / nranks_));  // one cooperative launch: keep it resident
+    for (auto& a : per_rank) {
+        // Everything that must be equal on every rank for the kernels to meet: a rank that planned
+        // differently (another buffer kind, alignment or size) is told so by the first barrier.
+        a.plan_hash = plan_fingerprint({static_cast<unsigned long long>(last_.collective), static_cast<unsigned long long>(last_.algo),
+                                        static_cast<unsigned long long>(cfg.grid), static_cast<unsigned long long>(pack_bytes),
+                                        a.len, static_cast<unsigned long long>(a.shard_mode), static_cast<unsigned long long>(a.store_all),
+                                        a.user_in != nullptr, a.user_out != nullptr, static_cast<unsigned long long>(args.dtype),
+                                        static_cast<unsigned long long>(args.redop), nvls});
+    }
     try {
         if (loopback_) {
             DeviceGuard guard(local_[0].device);
             cfg.stream = args.streams[0];
             cfg.loop_ranks = nranks_;
-            // Emulated ranks run inside one cooperative launch; keep it resident.
-            cfg.grid = std::min(cfg.grid, std::max(1, 128 / nranks_));
             for (auto& l : local_) wait_previous(l, cfg.stream);
-            B2_CUDA(kernels::launch_reduce(args.dtype, args.redop, wide, nvls, per_rank.data(), cfg));
+            B2_CUDA(kernels::launch_reduce(args.dtype, args.redop, pack_bytes, nvls, per_rank.data(), cfg));
             for (auto& l : local_) record_done(l, cfg.stream);
         } else {
             for (std::size_t i = 0; i < local_.size(); ++i) {
                 DeviceGuard guard(local_[i].device);
                 cfg.stream = args.streams[i];
                 wait_previous(local_[i], cfg.stream);
-                B2_CUDA(kernels::launch_reduce(args.dtype, args.redop, wide, nvls, &per_rank[i], cfg));
+                B2_CUDA(kernels::launch_reduce(args.dtype, args.redop, pack_bytes, nvls, &per_rank[i], cfg));
                 record_done(local_[i], cfg.stream);
             }
         }
@@ -458,12 +500,16 @@ void Communicator::Impl::launch_gather_ranks(const CollectiveArgs& args, std::ve
     kernels::LaunchConfig cfg;
     cfg.grid = std::min(grid, dev::kMaxCtas);
     cfg.block = dev::kBlockThreads;
+    if (loopback_) cfg.grid = std::min(cfg.grid, std::max(1, 128 / nranks_));
+    for (auto& a : per_rank)
+        a.plan_hash = plan_fingerprint({static_cast<unsigned long long>(Collective::AllGather), static_cast<unsigned long long>(cfg.grid),
+                                        a.len, a.out_stride, static_cast<unsigned long long>(a.mode),
+                                        static_cast<unsigned long long>(a.pack_bytes), a.user_in != nullptr});
     try {
         if (loopback_) {
             DeviceGuard guard(local_[0].device);
             cfg.stream = args.streams[0];
             cfg.loop_ranks = nranks_;
-            cfg.grid = std::min(cfg.grid, std::max(1, 128 / nranks_));
             for (auto& l : local_) wait_previous(l, cfg.stream);
             B2_CUDA(kernels::launch_gather(per_rank.data(), cfg));
             for (auto& l : local_) record_done(l, cfg.stream);
@@ -548,7 +594,7 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
     if (plan.error.empty() && plan.algo == Algo::Nvls && (plan.stage_in || plan.stage_out)) {
         // The staging arena is allocated on first use; every rank learns together (the binding is
         // agreed between processes) whether it got a multicast alias. Without one, plan again.
-        ensure_staging();
+        ensure_staging(args);
         if (stage_->multicast_ptr() == nullptr) {
             shape.staging_multicast = false;
             plan = sched::make_plan(shape, forced_algo_, tuning_);
@@ -604,7 +650,26 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
         launch_low_latency(args);
         return;
     }
-    if (plan.stage_in || plan.stage_out) ensure_staging();
+    if (plan.algo == Algo::Copy) {
+        // One rank: input and output hold `count` elements for every collective.
+        Local& l = local_[0];
+        DeviceGuard guard(l.device);
+        cudaStream_t stream = args.streams[0];
+        try {
+            wait_previous(l, stream);
+            if (args.send_buffers[0] != args.recv_buffers[0])
+                B2_CUDA(kernels::launch_local_copy(args.send_buffers[0], args.recv_buffers[0], args.count * esz, plan.grid,
+                                                   l.status, stream));
+            record_done(l, stream);
+        } catch (const std::exception& e) {
+            poison(std::string("launch failed: ") + e.what());
+            throw;
+        }
+        last_.grid = plan.grid;
+        last_.block = 32;
+        return;
+    }
+    if (plan.stage_in || plan.stage_out) ensure_staging(args);
     switch (collective) {
         case Collective::AllReduce: launch_all_reduce(args, plan, wide, in_sym ? &in_loc : nullptr, out_sym ? &out_loc : nullptr); break;
         case Collective::ReduceScatter: launch_reduce_scatter(args, plan, wide, in_sym ? &in_loc : nullptr); break;
@@ -615,7 +680,7 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
 // Low-latency AllReduce: the ranks exchange {data, call number} words through receive areas in
 // symmetric memory; the user's buffers are only touched by their own rank.
 void Communicator::Impl::launch_low_latency(const CollectiveArgs& args) {
-    if (!ll_area_) ll_area_ = alloc_->allocate(kernels::ll_area_bytes(nranks_), "low-latency slots");
+    if (!ll_area_) throw std::runtime_error("low-latency all_reduce needs peer-mapped memory");
     std::vector<dev::LlArgs> per(local_.size());
     for (std::size_t i = 0; i < local_.size(); ++i) {
         dev::LlArgs& a = per[i];
@@ -660,13 +725,27 @@ void Communicator::Impl::launch_low_latency(const CollectiveArgs& args) {
 void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sched::Plan& plan, bool wide,
                                            const std::vector<Located>* in_win, const std::vector<Located>* out_win) {
     const std::size_t esz = dtype_size(args.dtype);
-    const std::size_t pack = wide ? 16 : esz;
-    const std::size_t total_packs = args.count * esz / pack;
-    const bool staged = plan.stage_in || plan.stage_out;
-    const std::size_t cap_packs = staged ? staging_half_ / pack : total_packs;
     const bool direct = direct_peer_pointers();
     const bool nvls = plan.algo == Algo::Nvls;
     const bool oneshot = plan.algo == Algo::OneShot;
+    // 256-bit accesses for the peer two-shot loop when every rank can tell, from facts all ranks
+    // share, that the peer-visible addresses are 32-byte aligned: the arena is; windows are used at
+    // one common offset; a single process sees every pointer. (Shard boundaries are counted in
+    // packs, so all ranks must use the same pack.)
+    bool wide32 = wide && tuning_.wide32 && plan.algo == Algo::TwoShot && (args.count * esz) % 32 == 0;
+    auto aligned32 = [](const void* p) { return (reinterpret_cast<std::uintptr_t>(p) & 31u) == 0; };
+    if (wide32 && !plan.stage_in) {
+        if (in_win != nullptr) wide32 = aligned32(static_cast<const char*>(windows_[(*in_win)[0].region].ptr[0]) + (*in_win)[0].offset);
+        else for (const void* p : args.send_buffers) wide32 = wide32 && aligned32(p);
+    }
+    if (wide32 && !plan.stage_out) {
+        if (out_win != nullptr) wide32 = aligned32(static_cast<const char*>(windows_[(*out_win)[0].region].ptr[0]) + (*out_win)[0].offset);
+        else for (const void* p : args.recv_buffers) wide32 = wide32 && aligned32(p);
+    }
+    const std::size_t pack = wide32 ? 32 : (wide ? 16 : esz);
+    const std::size_t total_packs = args.count * esz / pack;
+    const bool staged = plan.stage_in || plan.stage_out;
+    const std::size_t cap_packs = staged ? staging_half_ / pack : total_packs;
 
     for (std::size_t done = 0; done < total_packs; done += cap_packs) {
         const std::size_t len = std::min(cap_packs, total_packs - done);
@@ -702,7 +781,7 @@ void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sch
                                           : static_cast<char*>(windows_[(*out_win)[i].region].mc) + (*out_win)[i].offset + off;
             }
         }
-        launch_reduce_ranks(args, per, wide, nvls, plan.grid);
+        launch_reduce_ranks(args, per, static_cast<int>(pack), nvls, plan.grid);
     }
 }
 
@@ -738,7 +817,7 @@ void Communicator::Impl::launch_reduce_scatter(const CollectiveArgs& args, const
             if (plan.stage_in) a.user_in = static_cast<const char*>(args.send_buffers[i]) + off;
             if (nvls) a.mc_in = static_cast<const char*>(windows_[(*in_win)[i].region].mc) + (*in_win)[i].offset + off;
         }
-        launch_reduce_ranks(args, per, wide, nvls, plan.grid);
+        launch_reduce_ranks(args, per, static_cast<int>(pack), nvls, plan.grid);
     }
 }
 

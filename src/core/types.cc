@@ -44,6 +44,8 @@ const char* algo_name(Algo a) {
         case Algo::Nvls: return "nvls";
         case Algo::Ring: return "ring";
         case Algo::LowLatency: return "ll";
+        case Algo::Copy: return "copy";
+        case Algo::Pipeline: return "pipeline";
     }
     return "unknown";
 }
@@ -96,8 +98,8 @@ bool parse_algo(const char* text, Algo* out) {
     static const std::pair<const char*, Algo> t[] = {
         {"auto", Algo::Auto},       {"oneshot", Algo::OneShot}, {"twoshot", Algo::TwoShot},
         {"nvls", Algo::Nvls},       {"ring", Algo::Ring},       {"ring_simple", Algo::Ring},
-        {"ll", Algo::LowLatency}};
-    return parse_from(text, out, t, 7);
+        {"ll", Algo::LowLatency},   {"pipeline", Algo::Pipeline}};
+    return parse_from(text, out, t, 8);
 }
 
 bool parse_collective(const char* text, Collective* out) {

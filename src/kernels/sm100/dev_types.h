@@ -16,7 +16,7 @@ constexpr int kMaxCtas = 160;       // flag rows per rank; one row per CTA index
 constexpr int kBlockThreads = 512;  // direct kernels
 constexpr int kRingMaxChannels = 32;
 constexpr int kLlCtas = 8;                  // the low-latency kernel always runs this many CTAs per rank
-constexpr unsigned kLlMaxBytes = 32u << 10; // largest message it takes
+constexpr unsigned kLlMaxBytes = 128u << 10; // largest message it takes
 constexpr unsigned kLlMaxWords = kLlMaxBytes / 4;
 
 // Per-rank control block. It lives in symmetric memory: every rank can store into every other
@@ -34,7 +34,12 @@ struct ControlBlock {
     // 0 until this rank's first failure has been recorded (device-local atomic; the status
     // record itself is then written with plain stores into host memory).
     unsigned int fail_once;
-    unsigned int pad_[30];
+    // plan_hash[src]: fingerprint of the plan (algorithm, grid, pack width, staging) that rank `src`
+    // launched its current direct collective with. Written remotely by CTA 0 of `src` just before its
+    // first barrier signal; compared after that barrier, so that ranks whose plans differ end with a
+    // diagnostic instead of running out their waits.
+    unsigned long long plan_hash[kMaxRanks];
+    unsigned int pad_[14];
     // Low-latency AllReduce: calls seen so far by each of its (fixed number of) CTAs. Local only.
     unsigned long long ll_epoch[kLlCtas];
     // Ring/Simple step counters. *_tail / *_head follow nano-nccl's ownership rule
@@ -51,6 +56,7 @@ enum StatusCode : unsigned int {
     kStatusTimeout = 1,   // a bounded wait ran out
     kStatusAborted = 2,   // abort flag seen while waiting
     kStatusBadArgs = 3,   // index/bounds self-check failed (debug builds)
+    kStatusPlanMismatch = 4,  // a peer launched this collective with a different plan
 };
 
 // One per local rank, in pinned mapped host memory: the host reads it without touching the device.
@@ -84,6 +90,11 @@ struct CollArgs {
     unsigned long long in_stride;   // Blocks: distance between blocks in `in`
     unsigned long long uin_stride;  // Blocks: distance between blocks in `user_in`
     unsigned long long timeout_ns;
+    unsigned long long plan_hash;   // see ControlBlock::plan_hash; 0 = no check
+    // Debug builds: extents in packs of in[p] / out[p] (0 = unknown); an index beyond them is
+    // recorded as kStatusBadArgs and the access is skipped.
+    unsigned long long in_extent;
+    unsigned long long out_extent;
     float scale;        // multiplies the reduced value (1/N for avg, 1 otherwise)
     int rank;
     int nranks;
@@ -102,6 +113,7 @@ struct GatherArgs {
     unsigned long long len;         // packs per rank
     unsigned long long out_stride;  // packs between consecutive ranks' blocks in the output
     unsigned long long timeout_ns;
+    unsigned long long plan_hash;   // see ControlBlock::plan_hash; 0 = no check
     int rank;
     int nranks;
     int mode;        // 0 push (store own block into every out), 1 pull (load every in), 2 nvls

@@ -32,24 +32,45 @@ __device__ __forceinline__ const A& select_args(const A& one) { return one; }
 template <typename A>
 __device__ __forceinline__ const A& select_args(const LoopPack<A>& all) { return all.r[blockIdx.y]; }
 
-// Copies the packs first, first+stripe, ... below len, four loads in flight per thread.
-template <typename P>
+// Copies the packs first, first+stripe, ... below len, four loads in flight per thread. One side is
+// the caller's own buffer (16-byte aligned at most), the other the staging arena.
+template <typename P, bool kFromUser>
 __device__ __forceinline__ void copy_stripes(void* dst, u64 dst0, const void* src, u64 src0, u64 first, u64 len, u64 stripe) {
     for (u64 j = first; j < len; j += stripe * 4) {
         typename P::Raw v[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (j + (u64)u * stripe < len) v[u] = P::load(src, src0 + j + (u64)u * stripe);
+        for (int u = 0; u < 4; ++u) {
+            if (j + (u64)u * stripe < len) {
+                if constexpr (kFromUser) v[u] = P::load_user(src, src0 + j + (u64)u * stripe);
+                else v[u] = P::load(src, src0 + j + (u64)u * stripe);
+            }
+        }
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (j + (u64)u * stripe < len) P::store(dst, dst0 + j + (u64)u * stripe, v[u]);
+        for (int u = 0; u < 4; ++u) {
+            if (j + (u64)u * stripe < len) {
+                if constexpr (kFromUser) P::store(dst, dst0 + j + (u64)u * stripe, v[u]);
+                else P::store_user(dst, dst0 + j + (u64)u * stripe, v[u]);
+            }
+        }
     }
 }
 
-template <int N>
+// Packs in flight per thread and peer: fewer ranks, or narrower packs, leave room for more.
+template <int N, int kPackBytes>
 struct UnrollFor {
-    static constexpr int value = N == 0 ? 1 : (N >= 8 ? 1 : (N >= 4 ? 2 : (N >= 2 ? 4 : 8)));
+    static constexpr int k16 = N == 0 ? 1 : (N >= 8 ? 1 : (N >= 4 ? 2 : (N >= 2 ? 4 : 8)));
+    static constexpr int value = kPackBytes == 32 ? (k16 > 1 ? k16 / 2 : 1) : k16;
 };
+
+#if defined(B200CCL_DEBUG_BOUNDS)
+// Checking builds: an index beyond the extent that the host passed is recorded (first one wins) and
+// the access is skipped; the kernel still runs to its end, so no wait is left hanging.
+#define B2_IN_BOUNDS(index, extent, where_)                                                                    \
+    ((extent) == 0ull || (index) < (extent) ||                                                                \
+     (report_failure(a.status, own, nullptr, 0, kStatusBadArgs, (unsigned)rank, (where_), (index), 0ull), false))
+#else
+#define B2_IN_BOUNDS(index, extent, where_) true
+#endif
 
 // One template for one-shot / two-shot / ReduceScatter / NVLS; the differences are data:
 // shard_mode picks the range this rank reduces, store_all picks who receives the result.
@@ -61,7 +82,7 @@ reduce_kernel(const __grid_constant__ ParamT param) {
     constexpr int kElems = P::kElems;
     constexpr int NN = N > 0 ? N : kMaxRanks;
     // For the multimem variant the N slot carries the unroll factor (the rank count is a run-time value there).
-    constexpr int kU = kNvls ? (N > 0 ? N : 4) : UnrollFor<N>::value;
+    constexpr int kU = kNvls ? (N > 0 ? N : 4) : UnrollFor<N, P::kBytes>::value;
 
     __shared__ u64 s_epoch;
     const CollArgs& a = select_args(param);
@@ -90,13 +111,13 @@ reduce_kernel(const __grid_constant__ ParamT param) {
         for (int s = 0; s < nshards; ++s) {
             const u64 lo = shard_lo(s), len = shard_len(s);
             const u64 dst0 = lo + (u64)s * a.in_stride, src0 = lo + (u64)s * a.uin_stride;
-            copy_stripes<P>(stage, dst0, a.user_in, src0, first, len, stripe);
+            copy_stripes<P, true>(stage, dst0, a.user_in, src0, first, len, stripe);
         }
     }
 
     // 2. Every rank's input is ready (and every rank's previous use of `out` is over).
     ++epoch;
-    if (!cta_barrier_all_ranks(a.ctrl, rank, n, epoch, a.timeout_ns, a.status, 1u)) return;
+    if (!cta_barrier_all_ranks(a.ctrl, rank, n, epoch, a.timeout_ns, a.status, 1u, a.plan_hash)) return;
 
     // 3. Reduce the own shard.
     {
@@ -137,7 +158,7 @@ reduce_kernel(const __grid_constant__ ParamT param) {
 #pragma unroll
                 for (int u = 0; u < kU; ++u) {
                     const u64 jj = j + (u64)u * stripe;
-                    if (jj < len) {
+                    if (jj < len && B2_IN_BOUNDS(in0 + jj, a.in_extent, 30u)) {
 #pragma unroll
                         for (int p = 0; p < NN; ++p)
                             if (p < n) r[u][p] = P::load(a.in[p], in0 + jj);
@@ -146,7 +167,7 @@ reduce_kernel(const __grid_constant__ ParamT param) {
 #pragma unroll
                 for (int u = 0; u < kU; ++u) {
                     const u64 jj = j + (u64)u * stripe;
-                    if (jj < len) {
+                    if (jj < len && B2_IN_BOUNDS(in0 + jj, a.in_extent, 30u) && B2_IN_BOUNDS(out0 + jj, a.out_extent, 31u)) {
                         // Fixed order 0..n-1: every rank computes bit-identical results.
                         float acc[kElems];
                         P::unpack(r[u][0], acc);
@@ -190,7 +211,7 @@ reduce_kernel(const __grid_constant__ ParamT param) {
     if (a.user_out != nullptr) {
         for (int s = 0; s < nshards; ++s) {
             const u64 lo = shard_lo(s), len = shard_len(s);
-            copy_stripes<P>(a.user_out, lo, a.out[rank], lo, first, len, stripe);
+            copy_stripes<P, false>(a.user_out, lo, a.out[rank], lo, first, len, stripe);
         }
     }
     if (threadIdx.x == 0) own->epoch[blockIdx.x] = epoch;
@@ -225,7 +246,7 @@ gather_kernel(const __grid_constant__ ParamT param) {
         for (u64 j = first; j < a.len; j += stripe) store(stage, j, load(a.user_in, j));
     }
     ++epoch;
-    if (!cta_barrier_all_ranks(a.ctrl, rank, n, epoch, a.timeout_ns, a.status, 1u)) return;
+    if (!cta_barrier_all_ranks(a.ctrl, rank, n, epoch, a.timeout_ns, a.status, 1u, a.plan_hash)) return;
 
     if (a.mode == 0) {
         const u64 base = (u64)rank * a.out_stride;
@@ -290,7 +311,7 @@ cudaError_t launch_reduce_n(int nranks, const ParamT& param, const LaunchConfig&
         if (cfg.nvls_unroll >= 8) return launch(reduce_kernel<T, Op, 8, PackT, true, ParamT>, param, cfg);
         if (cfg.nvls_unroll <= 2) return launch(reduce_kernel<T, Op, 2, PackT, true, ParamT>, param, cfg);
         return launch(reduce_kernel<T, Op, 4, PackT, true, ParamT>, param, cfg);
-    } else if constexpr (PackT<T>::kBytes != 16) {
+    } else if constexpr (PackT<T>::kBytes < 16) {
         return launch(reduce_kernel<T, Op, 0, PackT, false, ParamT>, param, cfg);
     } else {
         switch (nranks) {
@@ -314,20 +335,27 @@ cudaError_t launch_reduce_op(RedOp op, int nranks, const ParamT& param, const La
     return cudaErrorInvalidValue;
 }
 
+template <typename T, typename ParamT>
+cudaError_t launch_reduce_pack(RedOp op, int pack_bytes, int n, const ParamT& param, const LaunchConfig& cfg) {
+    if (pack_bytes == 32) return launch_reduce_op<T, Wide32>(op, n, param, cfg);
+    if (pack_bytes == 16) return launch_reduce_op<T, Wide>(op, n, param, cfg);
+    return launch_reduce_op<T, Narrow>(op, n, param, cfg);
+}
+
 template <typename T>
-cudaError_t launch_reduce_t(RedOp op, bool wide, bool nvls, const CollArgs* args, const LaunchConfig& cfg) {
+cudaError_t launch_reduce_t(RedOp op, int pack_bytes, bool nvls, const CollArgs* args, const LaunchConfig& cfg) {
     const int n = args[0].nranks;
     if (cfg.loop_ranks > 0) {
         if (nvls || cfg.loop_ranks > kMaxRanks) return cudaErrorInvalidValue;
         LoopPack<CollArgs> pack;
         for (int r = 0; r < cfg.loop_ranks; ++r) pack.r[r] = args[r];
-        return wide ? launch_reduce_op<T, Wide>(op, n, pack, cfg) : launch_reduce_op<T, Narrow>(op, n, pack, cfg);
+        return launch_reduce_pack<T>(op, pack_bytes, n, pack, cfg);
     }
     if (nvls) {
-        if (!wide || (op != RedOp::Sum && op != RedOp::Avg)) return cudaErrorInvalidValue;
+        if (pack_bytes != 16 || (op != RedOp::Sum && op != RedOp::Avg)) return cudaErrorInvalidValue;
         return launch_reduce_n<T, OpAdd, Wide, true>(n, args[0], cfg);
     }
-    return wide ? launch_reduce_op<T, Wide>(op, n, args[0], cfg) : launch_reduce_op<T, Narrow>(op, n, args[0], cfg);
+    return launch_reduce_pack<T>(op, pack_bytes, n, args[0], cfg);
 }
 
 template <typename RawT>
@@ -343,12 +371,13 @@ cudaError_t launch_gather_t(const GatherArgs* args, const LaunchConfig& cfg) {
 
 }  // namespace
 
-cudaError_t launch_reduce(DType dtype, RedOp op, bool wide, bool nvls, const CollArgs* args,
+cudaError_t launch_reduce(DType dtype, RedOp op, int pack_bytes, bool nvls, const CollArgs* args,
                           const LaunchConfig& cfg) {
+    if (pack_bytes != 32 && pack_bytes != 16 && pack_bytes != static_cast<int>(dtype_size(dtype))) return cudaErrorInvalidValue;
     switch (dtype) {
-        case DType::Float: return launch_reduce_t<float>(op, wide, nvls, args, cfg);
-        case DType::Float16: return launch_reduce_t<__half>(op, wide, nvls, args, cfg);
-        case DType::BFloat16: return launch_reduce_t<__nv_bfloat16>(op, wide, nvls, args, cfg);
+        case DType::Float: return launch_reduce_t<float>(op, pack_bytes, nvls, args, cfg);
+        case DType::Float16: return launch_reduce_t<__half>(op, pack_bytes, nvls, args, cfg);
+        case DType::BFloat16: return launch_reduce_t<__nv_bfloat16>(op, pack_bytes, nvls, args, cfg);
     }
     return cudaErrorInvalidValue;
 }
@@ -496,7 +525,7 @@ extern "C" int b2_local_all_reduce_no_alloc(const void* const* inputs, void* con
     cfg.block = kBlockThreads;
     cfg.stream = s;
     cfg.loop_ranks = nranks;
-    st = kernels::launch_reduce(dt, op, wide, false, args, cfg);
+    st = kernels::launch_reduce(dt, op, static_cast<int>(pack), false, args, cfg);
     if (st != cudaSuccess) {
         kernels::set_last_error_message(std::string("b2_local_all_reduce_no_alloc: launch failed: ") + cudaGetErrorString(st));
         (void)cudaGetLastError();

@@ -18,9 +18,11 @@ struct LaunchConfig {
     int nvls_unroll = 4;  // multimem loads in flight per thread (2, 4 or 8)
 };
 
-// wide: 16-byte packs (all pointers 16-byte aligned, lengths in 16-byte units); else one element
-// per access. nvls: multimem kernels (sum/avg, wide only).
-cudaError_t launch_reduce(DType dtype, RedOp op, bool wide, bool nvls, const dev::CollArgs* args,
+// pack_bytes: what one thread moves per access and the unit of every length in `args`: 32 (256-bit
+// accesses; every peer-visible pointer 32-byte aligned, the caller's own staged buffers 16-byte
+// aligned), 16, or the element size (fallback for odd counts and unaligned buffers).
+// nvls: multimem kernels (sum/avg, 16-byte packs only).
+cudaError_t launch_reduce(DType dtype, RedOp op, int pack_bytes, bool nvls, const dev::CollArgs* args,
                           const LaunchConfig& cfg);
 cudaError_t launch_gather(const dev::GatherArgs* args, const LaunchConfig& cfg);
 

@@ -1,4 +1,4 @@
-// Low-latency AllReduce for small messages (up to 32 KiB): no barrier at all. Every rank stores
+// Low-latency AllReduce for small messages (up to 128 KiB): no barrier at all. Every rank stores
 // each 4-byte word of its input, paired with the number of this call, straight into a slot of
 // every rank's receive area (one 8-byte store, which arrives whole). A receiver spins on the slot
 // until the call number matches, so the data is its own "ready" flag and the whole exchange costs
@@ -78,49 +78,54 @@ __global__ void __launch_bounds__(kBlockThreads) ll_kernel(const __grid_constant
             st_slot(a.area[q] + slot, v, flag);
         }
     }
-    // 2. Collect: wait for every source's word, combine in rank order, write the result.
+    // 2. Collect: the slots of all sources are loaded together (n loads in flight), then only the
+    //    sources whose call number has not arrived yet are polled again; combine in rank order.
     bool ok = true;
     const u64 t0 = global_timer_ns();
+    const u64* own_area = a.area[rank] + parity * (u64)n * kLlMaxWords;
     for (unsigned w = first; ok && w < a.nwords; w += stride) {
-        float acc[Word<T>::kLanes];
-        for (int p = 0; ok && p < n; ++p) {
-            const u64* slot = a.area[rank] + (parity * (u64)n + (u64)p) * kLlMaxWords + w;
-            uint2 v = ld_slot(slot);
-            unsigned polls = 0;
-            while (v.y != flag) {
-                if ((++polls & 1023u) == 0u) {
-                    if (ld_volatile_u32(&a.own_ctrl->abort_flag) != 0u) {
-                        report_failure(a.status, a.own_ctrl, nullptr, 0, kStatusAborted, (unsigned)p, 20u, call, global_timer_ns() - t0);
-                        ok = false;
-                        break;
-                    }
-                    const u64 waited = global_timer_ns() - t0;
-                    if (waited > a.timeout_ns) {
-                        report_failure(a.status, a.own_ctrl, a.ctrl, n, kStatusTimeout, (unsigned)p, 20u, call, waited);
-                        ok = false;
-                        break;
-                    }
-                }
-                v = ld_slot(slot);
-            }
-            if (!ok) break;
-            float f[Word<T>::kLanes];
-            Word<T>::unpack(v.x, f);
-            if (p == 0) {
+        uint2 v[kMaxRanks];
+        unsigned pending = (1u << n) - 1u;
+        unsigned polls = 0;
+        while (pending != 0u) {
 #pragma unroll
-                for (int e = 0; e < Word<T>::kLanes; ++e) acc[e] = f[e];
-            } else {
+            for (int p = 0; p < kMaxRanks; ++p)
+                if (pending & (1u << p)) v[p] = ld_slot(own_area + (u64)p * kLlMaxWords + w);
+#pragma unroll
+            for (int p = 0; p < kMaxRanks; ++p)
+                if ((pending & (1u << p)) && v[p].y == flag) pending &= ~(1u << p);
+            if (pending != 0u && (++polls & 255u) == 0u) {
+                const unsigned who = (unsigned)(__ffs((int)pending) - 1);
+                if (ld_volatile_u32(&a.own_ctrl->abort_flag) != 0u) {
+                    report_failure(a.status, a.own_ctrl, nullptr, 0, kStatusAborted, who, 20u, call, global_timer_ns() - t0);
+                    ok = false;
+                    break;
+                }
+                const u64 waited = global_timer_ns() - t0;
+                if (waited > a.timeout_ns) {
+                    report_failure(a.status, a.own_ctrl, a.ctrl, n, kStatusTimeout, who, 20u, call, waited);
+                    ok = false;
+                    break;
+                }
+            }
+        }
+        if (!ok) break;
+        float acc[Word<T>::kLanes];
+        Word<T>::unpack(v[0].x, acc);
+#pragma unroll
+        for (int p = 1; p < kMaxRanks; ++p) {
+            if (p < n) {
+                float f[Word<T>::kLanes];
+                Word<T>::unpack(v[p].x, f);
 #pragma unroll
                 for (int e = 0; e < Word<T>::kLanes; ++e) acc[e] = Op::apply(acc[e], f[e]);
             }
         }
-        if (ok) {
-            if (a.scale != 1.0f) {
+        if (a.scale != 1.0f) {
 #pragma unroll
-                for (int e = 0; e < Word<T>::kLanes; ++e) acc[e] *= a.scale;
-            }
-            out[w] = Word<T>::pack(acc);
+            for (int e = 0; e < Word<T>::kLanes; ++e) acc[e] *= a.scale;
         }
+        out[w] = Word<T>::pack(acc);
     }
     // A CTA whose wait gave up leaves its counter alone: the communicator is poisoned anyway.
     if (__syncthreads_and(ok ? 1 : 0) && threadIdx.x == 0) a.own_ctrl->ll_epoch[blockIdx.x] = call;

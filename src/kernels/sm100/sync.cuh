@@ -57,7 +57,7 @@ __device__ __forceinline__ void report_failure(Status* status, ControlBlock* own
         status->code = code;  // written last: the host treats a non-zero code as "record complete"
         __threadfence_system();
     }
-    if (code == kStatusTimeout && ctrl != nullptr) {
+    if ((code == kStatusTimeout || code == kStatusPlanMismatch) && ctrl != nullptr) {
         for (int q = 0; q < nranks; ++q) st_relaxed_sys_u32(&ctrl[q]->abort_flag, 1u);
     }
 }
@@ -92,19 +92,39 @@ __device__ __forceinline__ bool wait_at_least(const unsigned long long* flag, un
 // waits for rank p. Everything the CTA stored before the call is visible to every rank's CTA
 // after it (release on the signal, acquire on the poll, bar.sync on both sides).
 // Returns false (to every thread of the CTA) when the wait gave up.
+// plan_hash != 0: CTA 0 also publishes the fingerprint of this launch's plan with the signal and
+// compares it with every peer's after the wait; a difference ends the collective on every rank
+// with kStatusPlanMismatch (the other CTAs leave through the abort word).
 __device__ __forceinline__ bool cta_barrier_all_ranks(ControlBlock* const* ctrl, int rank, int nranks,
                                                       unsigned long long epoch, unsigned long long timeout_ns,
-                                                      Status* status, unsigned int where) {
+                                                      Status* status, unsigned int where,
+                                                      unsigned long long plan_hash = 0ull) {
     __syncthreads();
     int ok = 1;
     if (threadIdx.x < (unsigned)nranks) {
         const int p = threadIdx.x;
+        const bool check = plan_hash != 0ull && blockIdx.x == 0;
+        if (check) st_relaxed_sys(&ctrl[p]->plan_hash[rank], plan_hash);
         st_release_sys(&ctrl[p]->barrier[blockIdx.x][rank], epoch);
         ok = wait_at_least(&ctrl[rank]->barrier[blockIdx.x][p], epoch, ctrl[rank], timeout_ns,
                            status, ctrl, nranks, (unsigned)p, where)
                  ? 1 : 0;
+        if (ok && check && ld_relaxed_sys(&ctrl[rank]->plan_hash[p]) != plan_hash) {
+            report_failure(status, ctrl[rank], ctrl, nranks, kStatusPlanMismatch, (unsigned)p, where, epoch, 0ull);
+            ok = 0;
+        }
     }
     return __syncthreads_and(ok) != 0;
+}
+
+// The two halves of a barrier, for pipelines that signal early and wait late. `word` selects one
+// of a CTA's monotonic counters in every rank's flag block: row[src] of rank dst is written by src.
+__device__ __forceinline__ void signal_all_ranks(unsigned long long* const* rows, int rank, int nranks,
+                                                 unsigned long long value) {
+    // Caller: one thread per destination rank (lane p < nranks), after a barrier that orders the
+    // CTA's (or warp group's) stores before this release.
+    const int p = threadIdx.x & 31;
+    if (p < nranks) st_release_sys(rows[p] + rank, value);
 }
 
 }  // namespace b200ccl::dev

@@ -1,6 +1,7 @@
 // Bulk asynchronous copies (TMA, untiled form) and the mbarrier that tracks them.
-// Only the plain form is used: global → shared::cta of this GPU's own memory, completion on an
-// mbarrier of the same CTA. No multicast qualifier appears anywhere in this library.
+// Only the plain forms are used: global → shared::cta (completion on an mbarrier of the same CTA)
+// and shared::cta → global (bulk async-group), both on this GPU's own memory. No multicast
+// qualifier appears anywhere in this library.
 // Both addresses must be 16-byte aligned and the size a multiple of 16 bytes.
 #pragma once
 
@@ -44,5 +45,22 @@ __device__ __forceinline__ void tma_load_bulk(void* smem_dst, const void* gmem_s
                  "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
                  : "memory");
 }
+
+// shared -> global bulk copy, tracked by the thread's bulk async-group.
+__device__ __forceinline__ void tma_store_bulk(void* gmem_dst, const void* smem_src, unsigned bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_addr(smem_src)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most kPending of the thread's bulk groups have not finished READING their source.
+template <int kPending>
+__device__ __forceinline__ void tma_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+// Waits until every bulk group of the thread has completed (its writes are performed).
+__device__ __forceinline__ void tma_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Orders this thread's earlier generic-proxy accesses before later async-proxy (TMA) accesses.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 }  // namespace b200ccl::dev

@@ -80,6 +80,8 @@ struct Wide {
     static __device__ __forceinline__ void store(void* base, unsigned long long i, Raw v) {
         st16(static_cast<uint4*>(base) + i, v);
     }
+    static __device__ __forceinline__ Raw load_user(const void* base, unsigned long long i) { return load(base, i); }
+    static __device__ __forceinline__ void store_user(void* base, unsigned long long i, Raw v) { store(base, i, v); }
     static __device__ __forceinline__ void unpack(const Raw& r, float (&f)[kElems]);
     static __device__ __forceinline__ Raw pack(const float (&f)[kElems]);
 };
@@ -130,6 +132,75 @@ __device__ __forceinline__ uint4 Wide<__nv_bfloat16>::pack(const float (&f)[8]) 
     return make_uint4(f2_to_b2(f[0], f[1]), f2_to_b2(f[2], f[3]), f2_to_b2(f[4], f[5]), f2_to_b2(f[6], f[7]));
 }
 
+// ---- Wide32 pack: 32 bytes, one 256-bit access (sm_100) on the peer-visible side ----------------
+struct Raw32 {
+    uint4 lo, hi;
+};
+__device__ __forceinline__ Raw32 ld32_stream(const void* p) {
+    Raw32 v;
+    asm volatile("ld.global.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x), "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void st32(void* p, const Raw32& v) {
+    asm volatile("st.global.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.lo.x), "r"(v.lo.y), "r"(v.lo.z),
+                 "r"(v.lo.w), "r"(v.hi.x), "r"(v.hi.y), "r"(v.hi.z), "r"(v.hi.w)
+                 : "memory");
+}
+
+template <typename T>
+struct Wide32 {
+    static constexpr int kElems = 32 / sizeof(T);
+    static constexpr int kBytes = 32;
+    using Raw = Raw32;
+    // Peer-visible buffers (32-byte aligned by contract): one 256-bit access.
+    static __device__ __forceinline__ Raw load(const void* base, unsigned long long i) {
+        return ld32_stream(static_cast<const char*>(base) + i * 32ull);
+    }
+    static __device__ __forceinline__ void store(void* base, unsigned long long i, const Raw& v) {
+        st32(static_cast<char*>(base) + i * 32ull, v);
+    }
+    // The caller's own buffers in the staging copies need only 16-byte alignment: two 128-bit accesses.
+    static __device__ __forceinline__ Raw load_user(const void* base, unsigned long long i) {
+        const uint4* q = static_cast<const uint4*>(base) + 2ull * i;
+        Raw v;
+        v.lo = ld16_stream(q);
+        v.hi = ld16_stream(q + 1);
+        return v;
+    }
+    static __device__ __forceinline__ void store_user(void* base, unsigned long long i, const Raw& v) {
+        uint4* q = static_cast<uint4*>(base) + 2ull * i;
+        st16(q, v.lo);
+        st16(q + 1, v.hi);
+    }
+    static __device__ __forceinline__ void unpack(const Raw& r, float (&f)[kElems]) {
+        constexpr int h = kElems / 2;
+        float a[h], b[h];
+        Wide<T>::unpack(r.lo, a);
+        Wide<T>::unpack(r.hi, b);
+#pragma unroll
+        for (int e = 0; e < h; ++e) {
+            f[e] = a[e];
+            f[h + e] = b[e];
+        }
+    }
+    static __device__ __forceinline__ Raw pack(const float (&f)[kElems]) {
+        constexpr int h = kElems / 2;
+        float a[h], b[h];
+#pragma unroll
+        for (int e = 0; e < h; ++e) {
+            a[e] = f[e];
+            b[e] = f[h + e];
+        }
+        Raw v;
+        v.lo = Wide<T>::pack(a);
+        v.hi = Wide<T>::pack(b);
+        return v;
+    }
+};
+
 // ---- Narrow pack: one element -------------------------------------------------------------
 template <typename T>
 struct Narrow {
@@ -142,6 +213,8 @@ struct Narrow {
     static __device__ __forceinline__ void store(void* base, unsigned long long i, Raw v) {
         static_cast<T*>(base)[i] = v;
     }
+    static __device__ __forceinline__ Raw load_user(const void* base, unsigned long long i) { return load(base, i); }
+    static __device__ __forceinline__ void store_user(void* base, unsigned long long i, Raw v) { store(base, i, v); }
     static __device__ __forceinline__ void unpack(const Raw& r, float (&f)[1]) { f[0] = Elem<T>::to_f(r); }
     static __device__ __forceinline__ Raw pack(const float (&f)[1]) { return Elem<T>::from_f(f[0]); }
 };

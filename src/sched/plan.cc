@@ -11,7 +11,7 @@
 namespace b200ccl::sched {
 
 namespace {
-constexpr std::size_t kLlPlanMaxBytes = 32u << 10;  // capacity of the low-latency receive slots
+constexpr std::size_t kLlPlanMaxBytes = 128u << 10;  // capacity of the low-latency receive slots
 }
 
 Tuning default_tuning() {
@@ -79,6 +79,7 @@ Tuning tuning_from_text(const std::string& text, const Tuning& base, const std::
         else if (key == "bytes_per_cta") t.bytes_per_cta = std::max<std::size_t>(bytes, 1);
         else if (key == "oneshot_bytes_per_cta") t.oneshot_bytes_per_cta = std::max<std::size_t>(bytes, 1);
         else if (key == "ll_max_bytes") t.ll_max_bytes = std::min(bytes, kLlPlanMaxBytes);
+        else if (key == "wide32") t.wide32 = bytes != 0;
         else throw std::invalid_argument(where + "unknown key '" + key + "'");
     }
     return t;
@@ -109,6 +110,7 @@ Tuning tuning_from_env() {
     t.bytes_per_cta = env::get_bytes("B200CCL_BYTES_PER_CTA", t.bytes_per_cta);
     t.oneshot_bytes_per_cta = env::get_bytes("B200CCL_ONESHOT_BYTES_PER_CTA", t.oneshot_bytes_per_cta);
     t.ll_max_bytes = std::min<std::size_t>(env::get_bytes("B200CCL_LL_MAX_BYTES", t.ll_max_bytes), kLlPlanMaxBytes);
+    t.wide32 = env::get_bool("B200CCL_WIDE32", t.wide32);
     return t;
 }
 
@@ -158,8 +160,11 @@ Plan make_plan(const CallShape& s, Algo forced, const Tuning& t) {
         return p;
     }
     if (s.nranks == 1) {
-        p.algo = Algo::OneShot;  // degenerates to a local copy (with the avg scale of 1)
-        p.grid = grid_for(bytes, t, 148);  // nothing to share the GPU with: one CTA per SM
+        // One rank: every collective is a copy of `count` elements. 16-byte aligned buffers go through
+        // the TMA bulk-copy kernel (one CTA per SM, capped by max_ctas); anything else through the
+        // element-wise path of the one-shot kernel, which degenerates to a local copy.
+        p.algo = s.wide ? Algo::Copy : Algo::OneShot;
+        p.grid = s.wide ? (cap < default_tuning().max_ctas ? cap : 148) : grid_for(bytes, t, 148);
         p.gather_mode = 1;
         return p;
     }
@@ -197,7 +202,7 @@ Plan make_plan(const CallShape& s, Algo forced, const Tuning& t) {
     // AllReduce
     const bool ll_fits = s.word_aligned && bytes <= kLlPlanMaxBytes && s.nranks >= 2;
     if (forced == Algo::LowLatency && !ll_fits) {
-        p.error = "algo ll takes 4-byte aligned all_reduce messages of at most 32 KiB";
+        p.error = "algo ll takes 4-byte aligned all_reduce messages of at most 128 KiB";
         return p;
     }
     if (forced == Algo::LowLatency || (forced == Algo::Auto && ll_fits && bytes <= t.ll_max_bytes)) {

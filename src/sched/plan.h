@@ -52,15 +52,18 @@ struct Tuning {
     std::size_t bytes_per_cta = 0;                 // work given to one CTA before another is added
     std::size_t oneshot_bytes_per_cta = 0;         // one-shot reads every peer's copy: spread it thinner
     // AllReduce messages up to this size use the low-latency kernel (0 = only when asked for;
-    // B200CCL_LL_MAX_BYTES; never above 32 KiB).
+    // B200CCL_LL_MAX_BYTES; never above 128 KiB).
     std::size_t ll_max_bytes = 0;
+    // Peer two-shot AllReduce moves 32 bytes per access (ld/st.global.v8, sm_100) where alignment allows
+    // (B200CCL_WIDE32=0 keeps 16-byte accesses).
+    bool wide32 = true;
 };
 Tuning default_tuning();
 // default_tuning(), then the file named by B200CCL_TUNING_FILE (if set), then the B200CCL_* variables.
 Tuning tuning_from_env();
 // Applies a tuning file to `base`. One `key = value` per line, `#` starts a comment; byte counts take
 // K/M/G suffixes. Keys: oneshot_max_bytes (all rank counts) or oneshot_max_bytes.<nranks>, nvls_min_bytes,
-// max_ctas, nvls_max_ctas, twoshot_max_ctas, nvls_unroll, bytes_per_cta, oneshot_bytes_per_cta, ll_max_bytes.
+// max_ctas, nvls_max_ctas, twoshot_max_ctas, nvls_unroll, bytes_per_cta, oneshot_bytes_per_cta, ll_max_bytes, wide32.
 // `python -m nano_nccl_b200.tuner --emit-tuning FILE` writes such a file from its measurements.
 // Throws std::invalid_argument naming the file and line on an unknown key or a bad value.
 Tuning tuning_from_text(const std::string& text, const Tuning& base, const std::string& origin);

@@ -69,10 +69,10 @@ def test_planner_low_latency(lib, monkeypatch):
     assert rc == 0 and p[0] == 1  # off unless asked for
     rc, p = _plan(lib, 0, 1024, WORD, forced=5)
     assert rc == 0 and p[0] == 5 and p[1] == 8 and p[2] == 0 and p[3] == 0  # no staging even for private buffers
-    rc, p = _plan(lib, 0, 8192, WORD, forced=5)
-    assert rc == 0 and p[0] == 5  # 32 KiB of floats still fits
-    rc, p = _plan(lib, 0, 8193, WORD, forced=5)
-    assert rc == 2 and b"32 KiB" in lib.b2_last_error()
+    rc, p = _plan(lib, 0, 32768, WORD, forced=5)
+    assert rc == 0 and p[0] == 5  # 128 KiB of floats still fits
+    rc, p = _plan(lib, 0, 32769, WORD, forced=5)
+    assert rc == 2 and b"128 KiB" in lib.b2_last_error()
     rc, p = _plan(lib, 0, 1024, WIDE, forced=5)
     assert rc == 2  # not 4-byte aligned
     rc, p = _plan(lib, 1, 1024, WIDE | RD | WR | WORD, forced=5)
@@ -83,9 +83,9 @@ def test_planner_low_latency(lib, monkeypatch):
     rc, p = _plan(lib, 0, 4097 + 3, WIDE | RD | WR | WORD)
     assert rc == 0 and p[0] != 5  # above the threshold: the usual choice
     monkeypatch.setenv("B200CCL_LL_MAX_BYTES", "1M")  # clamped to the slot capacity
-    rc, p = _plan(lib, 0, 8192, WIDE | RD | WR | WORD)
+    rc, p = _plan(lib, 0, 32768, WIDE | RD | WR | WORD)
     assert rc == 0 and p[0] == 5
-    rc, p = _plan(lib, 0, 16384, WIDE | RD | WR | WORD)
+    rc, p = _plan(lib, 0, 65536, WIDE | RD | WR | WORD)
     assert rc == 0 and p[0] != 5
 
 
@@ -162,7 +162,7 @@ def test_tuning_file_from_tuner_tables():
         t = {"ll": 5 if size <= 2048 else 50, "oneshot": 8 if size <= 8192 else 80 + size / 1e4,
              "twoshot": 10 + size / 1e5, "nvls": 12 + size / 2e5 if size >= 1 << 20 else 14 + size / 1e5}
         for algo, us in t.items():
-            if algo == "ll" and size > 32768:
+            if algo == "ll" and size > 131072:
                 continue
             for ctas in (48, 64):
                 rows.append({"collective": "all_reduce", "algo": algo, "requested": algo, "max_ctas": ctas, "bytes": size,

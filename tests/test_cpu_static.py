@@ -72,8 +72,10 @@ def test_low_latency_kernel_waits_are_bounded_and_flags_travel_with_the_data():
     ll = read(os.path.join(KERNELS, "ll_allreduce.cu"))
     # one 8-byte store carries data and call number; one 8-byte load polls them
     assert "st.relaxed.sys.global.v2.u32" in ll and "ld.relaxed.sys.global.v2.u32" in ll
-    spin = ll[ll.index("while (v.y != flag)"):]
-    spin = spin[:spin.index("float f[")]
+    spin = ll[ll.index("while (pending != 0u)"):]
+    spin = spin[:spin.index("float acc[")]
+    # all sources' slots are loaded before the first comparison, so the polls overlap
+    assert spin.index("ld_slot(") < spin.index("== flag")
     assert "abort_flag" in spin and "timeout_ns" in spin and "kStatusTimeout" in spin and spin.count("break;") >= 2
     assert "cooperative" in ll.lower(), "emulated ranks wait on one another: they must share one cooperative launch"
 

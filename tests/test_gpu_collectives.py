@@ -94,7 +94,7 @@ def test_low_latency_all_reduce(comms, ranks, dtype):
     # the per-CTA call counters are exercised with different word ranges), every operator, in place.
     comm = comms(ranks, algo="ll")
     esz = torch.empty(0, dtype=dtype).element_size()
-    sizes = [4 // esz, 4096 // esz + 2, (32 << 10) // esz, 2, 1026, 8 // esz, (32 << 10) // esz]
+    sizes = [4 // esz, 4096 // esz + 2, (32 << 10) // esz, 2, 1026, 8 // esz, (128 << 10) // esz, (32 << 10) // esz]
     for i, numel in enumerate(sizes):
         op = ["sum", "avg", "max", "min"][i % 4]
         inputs = make_inputs(ranks, numel, dtype, seed=100 + i)
@@ -117,8 +117,8 @@ def test_low_latency_all_reduce(comms, ranks, dtype):
 
 def test_low_latency_limits_and_mixing(comms):
     comm = comms(4, algo="ll")
-    big = make_inputs(4, (32 << 10) // 4 + 1, torch.float32, seed=1)
-    with pytest.raises(Exception, match="32 KiB"):
+    big = make_inputs(4, (128 << 10) // 4 + 1, torch.float32, seed=1)
+    with pytest.raises(Exception, match="128 KiB"):
         comm.all_reduce([torch.empty_like(t) for t in big], big)
     odd = make_inputs(4, 3, torch.bfloat16, seed=1)  # 6 bytes: not a whole number of words
     with pytest.raises(Exception, match="4-byte"):
