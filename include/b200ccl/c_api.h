@@ -66,8 +66,8 @@ int b2_comm_check_async_error(const b2_comm* comm);
  * rank; streams are cudaStream_t values. */
 int b2_collective(b2_comm* comm, int collective, const void* const* send, void* const* recv,
                   void* const* streams, size_t count, int dtype, int redop, int allow_in_place);
-/* What the last call resolved to: algo, grid, block, staged_in, staged_out, vectorized. */
-int b2_comm_last_call(const b2_comm* comm, int out[6]);
+/* What the last call resolved to: algo, grid, block, staged_in, staged_out, vectorized, pack_bytes. */
+int b2_comm_last_call(const b2_comm* comm, int out[7]);
 
 /* Symmetric heap: `ptrs` receives one pointer per local rank. Collective over all processes. */
 int b2_comm_alloc_symmetric(b2_comm* comm, size_t bytes, void** ptrs);

@@ -64,6 +64,7 @@ struct CallInfo {
     bool staged_in = false;   // input went through the staging arena
     bool staged_out = false;  // output went through the staging arena
     bool vectorized = false;  // 16-byte path (false → scalar fallback for odd sizes/alignments)
+    int pack_bytes = 0;       // bytes one thread moves per access: 32, 16 or the element size (0: not applicable)
 };
 
 class Communicator {

@@ -108,10 +108,10 @@ class Communicator:
         return buf.value.decode()
 
     def last_call(self):
-        out = (ctypes.c_int * 6)()
+        out = (ctypes.c_int * 7)()
         self._lib.b2_comm_last_call(self._handle, out)
         return {"algo": _ALGO_NAMES[out[0]], "grid": out[1], "block": out[2], "staged_in": bool(out[3]),
-                "staged_out": bool(out[4]), "vectorized": bool(out[5])}
+                "staged_out": bool(out[4]), "vectorized": bool(out[5]), "pack_bytes": out[6]}
 
     def check_async_error(self):
         _lib.check(self._lib.b2_comm_check_async_error(self._handle))

@@ -148,7 +148,7 @@ int b2_collective(b2_comm* c, int collective, const void* const* send, void* con
     });
 }
 
-int b2_comm_last_call(const b2_comm* c, int out[6]) {
+int b2_comm_last_call(const b2_comm* c, int out[7]) {
     const CallInfo i = c->comm->last_call();
     out[0] = static_cast<int>(i.algo);
     out[1] = i.grid;
@@ -156,6 +156,7 @@ int b2_comm_last_call(const b2_comm* c, int out[6]) {
     out[3] = i.staged_in;
     out[4] = i.staged_out;
     out[5] = i.vectorized;
+    out[6] = i.pack_bytes;
     return 0;
 }
 

@@ -21,6 +21,7 @@
 #include "kernels/sm100/direct_collectives.h"
 #include "kernels/sm100/ll_allreduce.h"
 #include "kernels/sm100/local_copy.h"
+#include "kernels/sm100/staged_pipeline.h"
 #include "mem/ipc_window.h"
 #include "mem/symmetric.h"
 #include "sched/plan.h"
@@ -109,6 +110,7 @@ private:
                              bool nvls, int grid);
     void launch_gather_ranks(const CollectiveArgs& args, std::vector<dev::GatherArgs>& per_rank, int grid);
     void launch_low_latency(const CollectiveArgs& args);
+    void launch_pipeline(const CollectiveArgs& args, const sched::Plan& plan);
     bool direct_peer_pointers() const { return loopback_ || (!multiprocess_ && resolved_ == TransportKind::P2p); }
     void poison(const std::string& why) const {
         if (latched_.empty()) latched_ = why;
@@ -132,6 +134,7 @@ private:
     std::unique_ptr<mem::SymmetricAllocator> alloc_;
     std::unique_ptr<mem::SymmetricRegion> ctrl_;
     std::unique_ptr<mem::SymmetricRegion> stage_;
+    std::unique_ptr<mem::SymmetricRegion> pipe_flags_;  // dev::PipeFlags per rank, allocated with the arena
     std::unique_ptr<mem::SymmetricRegion> ll_area_;  // receive slots of the low-latency kernel (first use)
     // A window is a buffer that exists on every rank and that every rank can address: a symmetric
     // allocation (with a multicast alias where available) or a registered ordinary buffer.
@@ -309,6 +312,7 @@ Communicator::Impl::~Impl() {
     }
     ring_.reset();
     windows_.clear();
+    pipe_flags_.reset();
     stage_.reset();
     ll_area_.reset();
     ctrl_.reset();
@@ -361,6 +365,7 @@ void Communicator::Impl::ensure_staging(const CollectiveArgs& args) {
                                      "buffers of this kind before capturing, or use symmetric or registered buffers");
     }
     stage_ = alloc_->allocate(staging_half_ * 2, "staging");
+    pipe_flags_ = alloc_->allocate(sizeof(dev::PipeFlags), "pipeline flags");
 }
 
 Located Communicator::Impl::locate(const void* p, std::size_t bytes, int grank) const {
@@ -670,6 +675,10 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
         return;
     }
     if (plan.stage_in || plan.stage_out) ensure_staging(args);
+    if (plan.algo == Algo::Pipeline) {
+        launch_pipeline(args, plan);
+        return;
+    }
     switch (collective) {
         case Collective::AllReduce: launch_all_reduce(args, plan, wide, in_sym ? &in_loc : nullptr, out_sym ? &out_loc : nullptr); break;
         case Collective::ReduceScatter: launch_reduce_scatter(args, plan, wide, in_sym ? &in_loc : nullptr); break;
@@ -720,6 +729,80 @@ void Communicator::Impl::launch_low_latency(const CollectiveArgs& args) {
     }
     last_.grid = dev::kLlCtas;
     last_.block = dev::kBlockThreads;
+}
+
+// Pipelined staged AllReduce: one launch per rank, whatever the message size (the arena is a ring).
+void Communicator::Impl::launch_pipeline(const CollectiveArgs& args, const sched::Plan& plan) {
+    const std::size_t bytes = args.count * dtype_size(args.dtype);
+    kernels::PipeLaunch cfg;
+    cfg.grid = std::min(plan.grid, dev::kMaxCtas);
+    if (loopback_) {
+        // One cooperative launch plays every rank: all its CTAs must be resident at once.
+        int device = local_[0].device, sms = 0;
+        B2_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        cfg.grid = std::min(cfg.grid, std::max(1, sms / nranks_ - 1));  // the peer-load variant fits one CTA per SM
+    }
+    // Tiles and slots must fit the arena half: grid * slots * tile <= half, with at least two slots.
+    std::size_t tile = plan.tile_bytes;
+    while (tile > 4096 && static_cast<std::size_t>(cfg.grid) * 2 * tile > staging_half_) tile /= 2;
+    tile = tile / 16 * 16;
+    if (tile == 0 || static_cast<std::size_t>(cfg.grid) * 2 * tile > staging_half_)
+        throw std::invalid_argument("all_reduce: the staging arena is too small for the tile pipeline (B200CCL_STAGING_BYTES)");
+    const int slots = static_cast<int>(std::min<std::size_t>(4, staging_half_ / (static_cast<std::size_t>(cfg.grid) * tile)));
+    cfg.nvls = plan.pipe_nvls && !loopback_ && stage_->multicast_ptr() != nullptr;
+    cfg.nvls_unroll = tuning_.nvls_unroll;
+    std::vector<dev::PipeArgs> per(local_.size());
+    for (std::size_t i = 0; i < local_.size(); ++i) {
+        dev::PipeArgs& a = per[i];
+        std::memset(&a, 0, sizeof(a));
+        a.user_in = args.send_buffers[i];
+        a.user_out = args.recv_buffers[i];
+        for (int p = 0; p < nranks_; ++p) {
+            a.arena_in[p] = stage_->rank_ptr(p);
+            a.arena_out[p] = static_cast<char*>(stage_->rank_ptr(p)) + staging_half_;
+            a.ctrl[p] = static_cast<dev::ControlBlock*>(ctrl_->rank_ptr(p));
+            a.flags[p] = static_cast<dev::PipeFlags*>(pipe_flags_->rank_ptr(p));
+        }
+        if (cfg.nvls) {
+            a.mc_in = stage_->multicast_ptr();
+            a.mc_out = static_cast<char*>(stage_->multicast_ptr()) + staging_half_;
+        }
+        a.status = local_[i].status;
+        a.bytes = bytes;
+        a.tile_bytes = tile;
+        a.timeout_ns = timeout_ns_;
+        a.scale = args.redop == RedOp::Avg ? 1.0f / static_cast<float>(nranks_) : 1.0f;
+        a.rank = local_[i].grank;
+        a.nranks = nranks_;
+        a.slots = slots;
+        a.plan_hash = plan_fingerprint({static_cast<unsigned long long>(Algo::Pipeline), static_cast<unsigned long long>(cfg.grid), bytes, tile,
+                                        static_cast<unsigned long long>(slots), cfg.nvls, static_cast<unsigned long long>(args.dtype),
+                                        static_cast<unsigned long long>(args.redop)});
+    }
+    try {
+        if (loopback_) {
+            DeviceGuard guard(local_[0].device);
+            cfg.stream = args.streams[0];
+            cfg.loop_ranks = nranks_;
+            for (auto& l : local_) wait_previous(l, cfg.stream);
+            B2_CUDA(kernels::launch_staged_pipeline(args.dtype, args.redop, per.data(), cfg));
+            for (auto& l : local_) record_done(l, cfg.stream);
+        } else {
+            for (std::size_t i = 0; i < local_.size(); ++i) {
+                DeviceGuard guard(local_[i].device);
+                cfg.stream = args.streams[i];
+                wait_previous(local_[i], cfg.stream);
+                B2_CUDA(kernels::launch_staged_pipeline(args.dtype, args.redop, &per[i], cfg));
+                record_done(local_[i], cfg.stream);
+            }
+        }
+    } catch (const std::exception& e) {
+        poison(std::string("launch failed: ") + e.what());
+        throw;
+    }
+    last_.grid = cfg.grid;
+    last_.block = 512;
+    last_.pack_bytes = 16;
 }
 
 void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sched::Plan& plan, bool wide,
@@ -781,6 +864,7 @@ void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sch
                                           : static_cast<char*>(windows_[(*out_win)[i].region].mc) + (*out_win)[i].offset + off;
             }
         }
+        last_.pack_bytes = static_cast<int>(pack);
         launch_reduce_ranks(args, per, static_cast<int>(pack), nvls, plan.grid);
     }
 }

@@ -1,0 +1,360 @@
+// AllReduce of buffers that peers cannot address (ordinary allocations of another process), as a
+// three-stage tile pipeline inside ONE kernel per rank:
+//
+//   copy-in   one elected thread moves tile k of the caller's input into this rank's staging arena
+//             with TMA bulk copies (global -> shared -> global, own memory only),
+//   reduce    fourteen warps reduce this rank's shard of tile k across all ranks' arenas and store
+//             the result into every rank's arena: multimem.ld_reduce / multimem.st through the
+//             NVSwitch, or plain peer loads and stores (two ranks, max/min, no multicast),
+//   copy-out  one elected thread moves tile k of this rank's arena into the caller's output, again
+//             with TMA bulk copies,
+//
+// all three running at once on different tiles. The stages of the same CTA index on every rank
+// meet through three monotonic counters per (CTA, source rank) in peer memory (PipeFlags), written
+// with st.release.sys and polled with ld.acquire.sys: "tile copied in", "shard reduced and stored
+// everywhere", "tile copied out". A slot of the arena is reused once the counter that marks its last
+// reader has passed. The arena is a ring, so a message of any size streams through it in one launch.
+//
+// What is fused into the one launch: both staging copies, the cross-GPU synchronisation, the loads
+// from every rank, the fp32 widening and accumulation, the avg 1/N scale, the single rounding and
+// the broadcast of the result.
+//
+// The reference has no counterpart: it is single-process, so every buffer is peer-addressable, and
+// it moves data through per-edge FIFOs (src/kernels/ring_simple_kernel.cuh:1170-1230). The nearest
+// relative is its pivot step, which reduces, scales, writes the output and forwards in one pass
+// (kernel:433-481); here that pass is the reduce stage.
+#include "kernels/sm100/staged_pipeline.h"
+
+#include "kernels/sm100/sync.cuh"
+#include "kernels/sm100/tma.cuh"
+#include "kernels/sm100/vec.cuh"
+
+namespace b200ccl::kernels {
+
+using namespace b200ccl::dev;
+
+namespace {
+
+using u64 = unsigned long long;
+using uchar = unsigned char;
+
+constexpr int kThreads = 512;
+constexpr int kCopyWarps = 2;                               // warp 0 copies in, warp 1 copies out
+constexpr int kReduceThreads = kThreads - 32 * kCopyWarps;  // 448
+constexpr int kStages = 3;                                  // shared-memory stages per copy direction
+constexpr unsigned kChunk = 16384;                          // bytes per TMA bulk copy
+constexpr unsigned kPolls = 1u << 20;                       // bound on waiting for an own bulk copy
+
+struct CopyRing {
+    alignas(128) uchar tile[kStages][kChunk];
+    alignas(8) u64 full[kStages];
+};
+
+struct Shared {
+    CopyRing in;
+    CopyRing out;
+    int reduce_ok;
+    int failed;
+};
+
+template <typename A>
+__device__ __forceinline__ const A& select_args(const A& one) { return one; }
+template <typename A>
+__device__ __forceinline__ const A& select_args(const LoopPack<A>& all) { return all.r[blockIdx.y]; }
+
+__device__ __forceinline__ void reducers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kReduceThreads) : "memory"); }
+
+// Copies `bytes` from src to dst (both global, this GPU's own memory, 16-byte aligned, size a
+// multiple of 16) through the ring, driven by the calling thread alone. `done` counts the chunks
+// this ring has carried so far; it selects the stage and the mbarrier parity. Every stage is free
+// on entry and on return, and on return every store has completed. False: an own copy did not
+// land within the bound (copies still in flight were given a bounded time to land).
+__device__ bool bulk_copy(CopyRing& ring, u64& done, const uchar* src, uchar* dst, u64 bytes) {
+    const u64 n = (bytes + kChunk - 1) / kChunk;
+    auto chunk_bytes = [&](u64 i) {
+        const u64 off = i * kChunk;
+        return (unsigned)(bytes - off < kChunk ? bytes - off : kChunk);
+    };
+    auto load = [&](u64 i) {
+        const int s = (int)((done + i) % kStages);
+        mbar_arrive_expect_tx(&ring.full[s], chunk_bytes(i));
+        tma_load_bulk(ring.tile[s], src + i * kChunk, chunk_bytes(i), &ring.full[s]);
+    };
+    u64 loaded = n < (u64)kStages ? n : (u64)kStages;
+    for (u64 i = 0; i < loaded; ++i) load(i);
+    bool ok = true;
+    u64 i = 0;
+    for (; i < n; ++i) {
+        const u64 g = done + i;
+        const int s = (int)(g % kStages);
+        if (!mbar_wait_bounded(&ring.full[s], (unsigned)((g / kStages) & 1), kPolls)) {
+            ok = false;
+            break;
+        }
+        tma_store_bulk(dst + i * kChunk, ring.tile[s], chunk_bytes(i));
+        tma_commit_group();
+        if (i >= 1 && loaded < n) {
+            tma_wait_group_read<1>();  // the store before the newest has read its stage: refill it
+            load(loaded++);
+        }
+    }
+    if (!ok)
+        for (u64 k = i + 1; k < loaded; ++k) mbar_wait_bounded(&ring.full[(done + k) % kStages], (unsigned)(((done + k) / kStages) & 1), kPolls);
+    tma_wait_group_all();
+    done += n;
+    return ok;
+}
+
+template <typename T, typename Op, bool kNvls, int kU, typename ParamT>
+__global__ void __launch_bounds__(kThreads) pipeline_kernel(const __grid_constant__ ParamT param) {
+    using P = Wide<T>;
+    constexpr int kElems = P::kElems;
+    extern __shared__ __align__(128) uchar smem_raw[];
+    Shared& sm = *reinterpret_cast<Shared*>(smem_raw);
+    __shared__ u64 s_epoch, s_base;
+
+    const PipeArgs& a = select_args(param);
+    const int n = a.nranks, rank = a.rank;
+    const unsigned cta = blockIdx.x;
+    ControlBlock* own = a.ctrl[rank];
+    PipeFlags* mine = a.flags[rank];
+    if (threadIdx.x == 0) {
+        s_epoch = own->epoch[cta];
+        s_base = mine->base[cta];
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&sm.in.full[s], 1);
+            mbar_init(&sm.out.full[s], 1);
+        }
+        mbar_fence_init();
+        sm.failed = 0;
+        sm.reduce_ok = 1;
+    }
+    __syncthreads();
+    const u64 epoch = s_epoch + 1;
+    const u64 base = s_base;
+
+    // Every rank is inside this call (so nobody still uses the arena for an earlier one) and
+    // launched it with the same plan.
+    if (!cta_barrier_all_ranks(a.ctrl, rank, n, epoch, a.timeout_ns, a.status, 50u, a.plan_hash)) return;
+
+    const u64 total_tiles = (a.bytes + a.tile_bytes - 1) / a.tile_bytes;
+    const u64 K = cta < total_tiles ? (total_tiles - cta + gridDim.x - 1) / gridDim.x : 0;  // tiles cta, cta + grid, ...
+    const u64 S = (u64)a.slots;
+    auto tile_off = [&](u64 k) { return ((u64)cta + k * gridDim.x) * a.tile_bytes; };
+    auto tile_len = [&](u64 k) {
+        const u64 off = tile_off(k);
+        return a.bytes - off < a.tile_bytes ? a.bytes - off : a.tile_bytes;
+    };
+    auto slot_off = [&](u64 k) { return ((u64)cta * S + (k % S)) * a.tile_bytes; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    bool ok = true;
+
+    if (warp == 0) {
+        // ---- copy-in: caller's input -> own arena ----------------------------------------------
+        u64 chunks = 0;
+        const uchar* src = static_cast<const uchar*>(a.user_in);
+        uchar* dst = static_cast<uchar*>(a.arena_in[rank]);
+        for (u64 k = 0; k < K; ++k) {
+            int good = 1;
+            // The slot held tile k - S: every rank must have finished reducing it.
+            if (k >= S && lane < n)
+                good = wait_at_least(&mine->reduced[cta][lane], base + k - S + 1, own, a.timeout_ns, a.status, a.ctrl, n,
+                                     (unsigned)lane, 51u) ? 1 : 0;
+            if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+            if (lane == 0) {
+                fence_proxy_async();
+                good = bulk_copy(sm.in, chunks, src + tile_off(k), dst + slot_off(k), tile_len(k)) ? 1 : 0;
+                if (!good) report_failure(a.status, own, a.ctrl, n, kStatusTimeout, (unsigned)rank, 52u, base + k, 0ull);
+                fence_proxy_async();
+            }
+            // (the vote also orders lane 0's completed copies before the other lanes' signals)
+            if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+            if (lane < n) st_release_sys(&a.flags[lane]->in_ready[cta][rank], base + k + 1);
+        }
+    } else if (warp == 1) {
+        // ---- copy-out: own arena -> caller's output ----------------------------------------------
+        u64 chunks = 0;
+        const uchar* src = static_cast<const uchar*>(a.arena_out[rank]);
+        uchar* dst = static_cast<uchar*>(a.user_out);
+        for (u64 k = 0; k < K; ++k) {
+            int good = 1;
+            if (lane < n)
+                good = wait_at_least(&mine->reduced[cta][lane], base + k + 1, own, a.timeout_ns, a.status, a.ctrl, n,
+                                     (unsigned)lane, 53u) ? 1 : 0;
+            if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+            if (lane == 0) {
+                fence_proxy_async();
+                good = bulk_copy(sm.out, chunks, src + slot_off(k), dst + tile_off(k), tile_len(k)) ? 1 : 0;
+                if (!good) report_failure(a.status, own, a.ctrl, n, kStatusTimeout, (unsigned)rank, 56u, base + k, 0ull);
+            }
+            if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+            if (lane < n) st_release_sys(&a.flags[lane]->drained[cta][rank], base + k + 1);
+        }
+    } else {
+        // ---- reduce: own shard of the tile, all ranks' arenas -> all ranks' arenas --------------------
+        const u64 rt = threadIdx.x - 32 * kCopyWarps;
+        const bool scaled = a.scale != 1.0f;
+        for (u64 k = 0; k < K; ++k) {
+            if (warp == kCopyWarps) {
+                int good = 1;
+                if (lane < n)  // every rank's copy of tile k is in its arena
+                    good = wait_at_least(&mine->in_ready[cta][lane], base + k + 1, own, a.timeout_ns, a.status, a.ctrl, n,
+                                         (unsigned)lane, 54u) ? 1 : 0;
+                else if (lane >= 16 && lane < 16 + n && k >= S)  // every rank has copied tile k - S out of the slot
+                    good = wait_at_least(&mine->drained[cta][lane - 16], base + k - S + 1, own, a.timeout_ns, a.status, a.ctrl,
+                                         n, (unsigned)(lane - 16), 55u) ? 1 : 0;
+                good = __all_sync(0xffffffffu, good);
+                if (lane == 0) sm.reduce_ok = good;
+            }
+            reducers_sync();
+            if (!sm.reduce_ok) { ok = false; break; }
+            const u64 packs = tile_len(k) / 16;
+            const u64 lo = packs * (u64)rank / (u64)n, hi = packs * (u64)(rank + 1) / (u64)n;
+            const u64 s0 = slot_off(k) / 16;
+            if constexpr (kNvls) {
+                const uint4* mc_in = static_cast<const uint4*>(a.mc_in) + s0;
+                uint4* mc_out = static_cast<uint4*>(a.mc_out) + s0;
+                for (u64 j = lo + rt; j < hi; j += (u64)kReduceThreads * kU) {
+                    uint4 r[kU];
+#pragma unroll
+                    for (int u = 0; u < kU; ++u) {
+                        const u64 jj = j + (u64)u * kReduceThreads;
+                        if (jj < hi) r[u] = multimem_ld_reduce_add<T>(mc_in + jj);
+                    }
+#pragma unroll
+                    for (int u = 0; u < kU; ++u) {
+                        const u64 jj = j + (u64)u * kReduceThreads;
+                        if (jj < hi) {
+                            uint4 v = r[u];
+                            if (scaled) {
+                                float f[kElems];
+                                P::unpack(v, f);
+#pragma unroll
+                                for (int e = 0; e < kElems; ++e) f[e] *= a.scale;
+                                v = P::pack(f);
+                            }
+                            multimem_st16(mc_out + jj, v);
+                        }
+                    }
+                }
+            } else {
+                for (u64 j = lo + rt; j < hi; j += (u64)kReduceThreads * kU) {
+                    uint4 r[kU][kMaxRanks];
+#pragma unroll
+                    for (int u = 0; u < kU; ++u) {
+                        const u64 jj = j + (u64)u * kReduceThreads;
+                        if (jj < hi) {
+#pragma unroll
+                            for (int p = 0; p < kMaxRanks; ++p)
+                                if (p < n) r[u][p] = P::load(a.arena_in[p], s0 + jj);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < kU; ++u) {
+                        const u64 jj = j + (u64)u * kReduceThreads;
+                        if (jj < hi) {
+                            float acc[kElems];  // fixed order 0..n-1: bit-identical results on every rank
+                            P::unpack(r[u][0], acc);
+#pragma unroll
+                            for (int p = 1; p < kMaxRanks; ++p) {
+                                if (p < n) {
+                                    float f[kElems];
+                                    P::unpack(r[u][p], f);
+#pragma unroll
+                                    for (int e = 0; e < kElems; ++e) acc[e] = Op::apply(acc[e], f[e]);
+                                }
+                            }
+                            if (scaled) {
+#pragma unroll
+                                for (int e = 0; e < kElems; ++e) acc[e] *= a.scale;
+                            }
+                            const uint4 v = P::pack(acc);
+#pragma unroll
+                            for (int q = 0; q < kMaxRanks; ++q) {
+                                if (q < n) {
+                                    int dstr = rank + q;  // start with the own copy, then spread over peers
+                                    if (dstr >= n) dstr -= n;
+                                    P::store(a.arena_out[dstr], s0 + jj, v);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            reducers_sync();  // every reducer's stores happen-before the release below
+            if (warp == kCopyWarps && lane < n) st_release_sys(&a.flags[lane]->reduced[cta][rank], base + k + 1);
+        }
+    }
+
+    if (!ok) *(volatile int*)&sm.failed = 1;
+    __syncthreads();
+    // Progress persists only when every stage ran to its end (a failed call leaves the communicator unusable).
+    if (threadIdx.x == 0 && *(volatile int*)&sm.failed == 0) {
+        own->epoch[cta] = epoch;
+        mine->base[cta] = base + K;
+    }
+}
+
+template <typename KernelT, typename ParamT>
+cudaError_t launch_kernel(KernelT kernel, const ParamT& param, const PipeLaunch& cfg) {
+    const std::size_t smem = sizeof(Shared);
+    // The attribute belongs to the current device's copy of the function: set it on every launch.
+    cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (st != cudaSuccess) return st;
+    dim3 grid(cfg.grid, cfg.loop_ranks > 0 ? cfg.loop_ranks : 1, 1), block(kThreads, 1, 1);
+    if (cfg.loop_ranks > 0) {
+        void* params[] = {const_cast<ParamT*>(&param)};
+        return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), grid, block, params, smem, cfg.stream);
+    }
+    kernel<<<grid, block, smem, cfg.stream>>>(param);
+    return cudaGetLastError();
+}
+
+template <typename T, typename Op>
+cudaError_t launch_peer(const PipeArgs* args, const PipeLaunch& cfg) {
+    if (cfg.loop_ranks > 0) {
+        if (cfg.loop_ranks > kMaxRanks) return cudaErrorInvalidValue;
+        LoopPack<PipeArgs> pack;
+        for (int r = 0; r < cfg.loop_ranks; ++r) pack.r[r] = args[r];
+        return launch_kernel(pipeline_kernel<T, Op, false, 2, LoopPack<PipeArgs>>, pack, cfg);
+    }
+    return launch_kernel(pipeline_kernel<T, Op, false, 2, PipeArgs>, args[0], cfg);
+}
+
+template <typename T>
+cudaError_t launch_t(RedOp op, const PipeArgs* args, const PipeLaunch& cfg) {
+    if (cfg.nvls) {
+        if (cfg.loop_ranks > 0 || (op != RedOp::Sum && op != RedOp::Avg) || args[0].mc_in == nullptr || args[0].mc_out == nullptr)
+            return cudaErrorInvalidValue;
+        // (Eight loads in flight per thread spill at the 64 registers that let two CTAs share an SM.)
+        if (cfg.nvls_unroll <= 2) return launch_kernel(pipeline_kernel<T, OpAdd, true, 2, PipeArgs>, args[0], cfg);
+        return launch_kernel(pipeline_kernel<T, OpAdd, true, 4, PipeArgs>, args[0], cfg);
+    }
+    switch (op) {
+        case RedOp::Sum:
+        case RedOp::Avg: return launch_peer<T, OpAdd>(args, cfg);
+        case RedOp::Max: return launch_peer<T, OpMax>(args, cfg);
+        case RedOp::Min: return launch_peer<T, OpMin>(args, cfg);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+std::size_t pipeline_smem_bytes() { return sizeof(Shared); }
+
+cudaError_t launch_staged_pipeline(DType dtype, RedOp op, const PipeArgs* args, const PipeLaunch& cfg) {
+    const PipeArgs& a = args[0];
+    if (a.bytes == 0 || a.bytes % 16 != 0 || a.tile_bytes == 0 || a.tile_bytes % 16 != 0 || a.slots < 1 || cfg.grid < 1 ||
+        cfg.grid > kMaxCtas)
+        return cudaErrorInvalidValue;
+    switch (dtype) {
+        case DType::Float: return launch_t<float>(op, args, cfg);
+        case DType::Float16: return launch_t<__half>(op, args, cfg);
+        case DType::BFloat16: return launch_t<__nv_bfloat16>(op, args, cfg);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace b200ccl::kernels

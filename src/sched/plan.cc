@@ -36,6 +36,9 @@ Tuning default_tuning() {
     t.twoshot_max_ctas = 128;
     t.bytes_per_cta = 32u << 10;
     t.oneshot_bytes_per_cta = 8u << 10;
+    t.pipeline_min_bytes = 1u << 20;
+    t.pipeline_tile_bytes = 256u << 10;
+    t.pipeline_max_ctas = 64;
     return t;
 }
 
@@ -80,6 +83,9 @@ Tuning tuning_from_text(const std::string& text, const Tuning& base, const std::
         else if (key == "oneshot_bytes_per_cta") t.oneshot_bytes_per_cta = std::max<std::size_t>(bytes, 1);
         else if (key == "ll_max_bytes") t.ll_max_bytes = std::min(bytes, kLlPlanMaxBytes);
         else if (key == "wide32") t.wide32 = bytes != 0;
+        else if (key == "pipeline_min_bytes") t.pipeline_min_bytes = bytes;
+        else if (key == "pipeline_tile_bytes") t.pipeline_tile_bytes = std::max<std::size_t>(bytes / 4096 * 4096, 32u << 10);
+        else if (key == "pipeline_max_ctas") t.pipeline_max_ctas = std::max(as_int, 1);
         else throw std::invalid_argument(where + "unknown key '" + key + "'");
     }
     return t;
@@ -111,6 +117,9 @@ Tuning tuning_from_env() {
     t.oneshot_bytes_per_cta = env::get_bytes("B200CCL_ONESHOT_BYTES_PER_CTA", t.oneshot_bytes_per_cta);
     t.ll_max_bytes = std::min<std::size_t>(env::get_bytes("B200CCL_LL_MAX_BYTES", t.ll_max_bytes), kLlPlanMaxBytes);
     t.wide32 = env::get_bool("B200CCL_WIDE32", t.wide32);
+    t.pipeline_min_bytes = env::get_bytes("B200CCL_PIPELINE_MIN_BYTES", t.pipeline_min_bytes);
+    t.pipeline_tile_bytes = std::max<std::size_t>(env::get_bytes("B200CCL_PIPELINE_TILE_BYTES", t.pipeline_tile_bytes) / 4096 * 4096, 32u << 10);
+    t.pipeline_max_ctas = std::max(1, static_cast<int>(env::get_int("B200CCL_PIPELINE_MAX_CTAS", t.pipeline_max_ctas)));
     return t;
 }
 
@@ -208,6 +217,25 @@ Plan make_plan(const CallShape& s, Algo forced, const Tuning& t) {
     if (forced == Algo::LowLatency || (forced == Algo::Auto && ll_fits && bytes <= t.ll_max_bytes)) {
         p.algo = Algo::LowLatency;  // neither buffer needs to be peer-addressable: no staging
         p.grid = 8;
+        return p;
+    }
+    // Buffers that peers cannot address, large enough for the tile pipeline: both sides pass through
+    // the staging arena (a side that peers could address is simply copied locally).
+    const bool needs_staging = !s.peers_read_input || !s.peers_write_output;
+    if (forced == Algo::Pipeline && !s.wide) {
+        p.error = "algo pipeline needs 16-byte aligned buffers and a message that is a multiple of 16 bytes";
+        return p;
+    }
+    if (forced == Algo::Pipeline || (forced == Algo::Auto && needs_staging && s.wide && bytes >= t.pipeline_min_bytes)) {
+        p.algo = Algo::Pipeline;
+        p.stage_in = p.stage_out = true;
+        p.pipe_nvls = s.staging_multicast && s.nranks >= 3 && (s.redop == RedOp::Sum || s.redop == RedOp::Avg);
+        const int grid_max = std::max(1, std::min(cap, t.pipeline_max_ctas));
+        std::size_t tile = std::max<std::size_t>(t.pipeline_tile_bytes, 32u << 10);
+        while (tile > (32u << 10) && bytes / tile < 2 * static_cast<std::size_t>(grid_max)) tile /= 2;
+        tile = tile / 4096 * 4096;
+        p.tile_bytes = tile;
+        p.grid = static_cast<int>(std::min<std::size_t>(static_cast<std::size_t>(grid_max), (bytes + tile - 1) / tile));
         return p;
     }
     Algo algo = forced;

@@ -37,6 +37,10 @@ struct Plan {
     bool stage_in = false;
     bool stage_out = false;
     int gather_mode = 0;  // AllGather: 0 push, 1 pull, 2 nvls
+    // Pipeline: bytes of one tile (CTA b owns tiles b, b + grid, ...) and whether its reduce stage
+    // goes through the switch (multimem) or over plain peer loads and stores.
+    std::size_t tile_bytes = 0;
+    bool pipe_nvls = false;
     std::string error;    // non-empty → the request cannot be satisfied (forced algo impossible)
 };
 
@@ -57,13 +61,21 @@ struct Tuning {
     // Peer two-shot AllReduce moves 32 bytes per access (ld/st.global.v8, sm_100) where alignment allows
     // (B200CCL_WIDE32=0 keeps 16-byte accesses).
     bool wide32 = true;
+    // AllReduce of buffers that peers cannot address: from this size up the copy into the staging arena,
+    // the reduction and the copy out run as a tile pipeline in one kernel (B200CCL_PIPELINE_MIN_BYTES;
+    // below it: copy, barrier, reduce, barrier, copy). Tiles of pipeline_tile_bytes, halved for small
+    // messages down to 32 KiB until every CTA has two; at most pipeline_max_ctas CTAs.
+    std::size_t pipeline_min_bytes = 0;
+    std::size_t pipeline_tile_bytes = 0;
+    int pipeline_max_ctas = 64;
 };
 Tuning default_tuning();
 // default_tuning(), then the file named by B200CCL_TUNING_FILE (if set), then the B200CCL_* variables.
 Tuning tuning_from_env();
 // Applies a tuning file to `base`. One `key = value` per line, `#` starts a comment; byte counts take
 // K/M/G suffixes. Keys: oneshot_max_bytes (all rank counts) or oneshot_max_bytes.<nranks>, nvls_min_bytes,
-// max_ctas, nvls_max_ctas, twoshot_max_ctas, nvls_unroll, bytes_per_cta, oneshot_bytes_per_cta, ll_max_bytes, wide32.
+// max_ctas, nvls_max_ctas, twoshot_max_ctas, nvls_unroll, bytes_per_cta, oneshot_bytes_per_cta, ll_max_bytes, wide32,
+// pipeline_min_bytes, pipeline_tile_bytes, pipeline_max_ctas.
 // `python -m nano_nccl_b200.tuner --emit-tuning FILE` writes such a file from its measurements.
 // Throws std::invalid_argument naming the file and line on an unknown key or a bad value.
 Tuning tuning_from_text(const std::string& text, const Tuning& base, const std::string& origin);
