@@ -12,10 +12,12 @@ per GPU. Prints ONE JSON line from rank 0.
     ... bench.py --impl nccl        # torch.distributed NCCL on the same buffers (comparator)
     ... bench.py --impl nccl-ring   # NCCL pinned to Ring + Simple, 4 channels, 32 MiB buffer
 
-Timing: W warm-up steps, then exactly K steps between a barrier + device synchronize on both
-sides, measured with CUDA events on the launching stream, maximum over ranks. Successive steps
-rotate over buffer sets whose total exceeds the 126 MB L2. SM clocks and throttle reasons are
-sampled with nvidia-smi during the timed region.
+Timing: W warm-up steps, then batches of exactly K steps, each batch between a barrier + device
+synchronize on both sides and measured with CUDA events on the launching stream, maximum over
+ranks; the batch is repeated (7 times by default) and the MEDIAN batch is reported, with the
+fastest and slowest beside it. Successive steps rotate over buffer sets whose total exceeds the
+126 MB L2. SM clocks and throttle reasons are sampled during the timed batches. A short sweep over
+message sizes is measured the same way and printed under "sweep".
 """
 import argparse
 import json
@@ -46,7 +48,9 @@ def parse_args():
                     help="symmetric: tensors from Communicator.empty (peer-mapped, NVLS-capable); plain: torch.empty "
                          "(staged inside the kernel); registered: torch.empty + Communicator.register (peer-mapped)")
     ap.add_argument("--algo", default="auto")
-    ap.add_argument("--sweep", action="store_true", help="also measure 1 KiB..1 GiB and add it under 'sweep'")
+    ap.add_argument("--repeats", type=int, default=7, help="timed batches of --steps steps; the median batch is reported")
+    ap.add_argument("--sweep", default="short", choices=["short", "full", "none"],
+                    help="short: 1 KiB, 64 KiB, 1 MiB, 16 MiB, 64 MiB, 1 GiB; full: every power of two from 1 KiB to --sweep-max")
     ap.add_argument("--sweep-max", type=int, default=1 << 30)
     ap.add_argument("--ref-transport", default="p2p", choices=["auto", "p2p", "shm"])
     return ap.parse_args()
@@ -85,6 +89,30 @@ def init_dist(backend):
 def busbw(nbytes, seconds, n):
     alg = nbytes / seconds / 1e9
     return alg * 2 * (n - 1) / n if n > 1 else alg
+
+
+def link_bytes_per_direction(algo, nbytes, n):
+    """Bytes that leave (and that enter) one GPU over NVLink for an AllReduce of nbytes per rank."""
+    if n < 2:
+        return 0.0
+    if algo in ("nvls",):            # every shard goes out once to the switch and the result comes back multicast
+        return nbytes * (1 + 1.0 / n)
+    if algo in ("twoshot", "ring"):  # pull the own shard from n-1 peers, push the result to n-1 peers
+        return nbytes * 2.0 * (n - 1) / n
+    if algo == "oneshot":            # every peer reads the whole message
+        return float(nbytes) * (n - 1)
+    if algo == "ll":                 # 8 bytes on the wire per 4 bytes of data, to every peer
+        return 2.0 * nbytes * (n - 1)
+    return nbytes * 2.0 * (n - 1) / n
+
+
+def measured_peaks():
+    """The machine's measured copy bandwidth (GB/s) if the file is there, else an earlier measurement."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
 
 
 def torch_dtype(name):
@@ -166,23 +194,40 @@ class Runner:
             sets.append((inp, out))
         return sets, numel, nsets * per_set
 
-    def time_steps(self, sets, op, warmup, steps):
+    def time_steps(self, sets, op, warmup, steps, repeats=1):
+        """W warm-up steps, then `repeats` batches of exactly `steps` steps. Returns the per-batch
+        seconds (each the maximum over ranks), in the order measured."""
         torch = self.torch
         for i in range(warmup):
             inp, out = sets[i % len(sets)]
             self.all_reduce(out, inp, op)
-        self.barrier()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        self.launches = 0
-        start.record()
-        for i in range(steps):
-            inp, out = sets[i % len(sets)]
-            self.all_reduce(out, inp, op)
-        stop.record()
-        self.barrier()
-        if self.comm is not None:
-            self.comm.check_async_error()
-        return self.max_over_ranks(start.elapsed_time(stop) / 1e3)
+        batches = []
+        for _ in range(repeats):
+            self.barrier()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.launches = 0
+            start.record()
+            for i in range(steps):
+                inp, out = sets[i % len(sets)]
+                self.all_reduce(out, inp, op)
+            stop.record()
+            self.barrier()
+            if self.comm is not None:
+                self.comm.check_async_error()
+            batches.append(self.max_over_ranks(start.elapsed_time(stop) / 1e3))
+        return batches
+
+    def release(self, sets):
+        """Gives symmetric / registered buffers back (a collective call, like their allocation)."""
+        if self.comm is None:
+            return
+        for inp, out in sets:
+            if self.args.buffers == "symmetric":
+                self.comm.free(inp)
+                self.comm.free(out)
+            elif self.args.buffers == "registered":
+                self.comm.unregister(inp)
+                self.comm.unregister(out)
 
     def verify(self, sets, numel, dtype, op):
         """Recomputes the expected result of set 0 from every rank's seeded input (fp32) and counts mismatches."""
@@ -241,6 +286,11 @@ class Runner:
         return self.max_over_ranks(start.elapsed_time(stop) / 1e3), h2d, d2h
 
 
+def median(values):
+    v = sorted(values)
+    return v[len(v) // 2] if len(v) % 2 else 0.5 * (v[len(v) // 2 - 1] + v[len(v) // 2])
+
+
 def run_measured(args):
     import torch
     r = Runner(args)
@@ -253,35 +303,47 @@ def run_measured(args):
         sampler.start()
         time.sleep(0.05)  # let the sampler come up before the timed region
     t_begin = time.time()
-    seconds = r.time_steps(sets, args.op, max(args.warmup, 3), args.steps)
+    batches = r.time_steps(sets, args.op, max(args.warmup, 3), args.steps, max(args.repeats, 1))
     t_end = time.time()
+    seconds = median(batches)
     launches = r.launches
     clocks = sampler.stop((t_begin, t_end)) if r.rank == 0 else None
-    e2e_seconds, h2d, d2h = r.time_e2e(sets, numel, dtype, args.op, max(args.warmup // 2, 3), max(args.steps // 4, 5))
-    e2e_steps = max(args.steps // 4, 5)
+    e2e_steps = args.steps
+    e2e_seconds, h2d, d2h = r.time_e2e(sets, numel, dtype, args.op, max(args.warmup, 3), e2e_steps)
     info = r.comm.last_call() if r.comm is not None else {"algo": args.impl}
+    r.release(sets)
+    del sets
+    torch.cuda.empty_cache()
 
     sweep = None
-    if args.sweep:
+    if args.sweep != "none":
         sweep = []
-        size = 1024
-        while size <= args.sweep_max:
+        if args.sweep == "short":
+            sizes = [s for s in (1 << 10, 64 << 10, 1 << 20, 16 << 20, 64 << 20, 1 << 30) if s <= args.sweep_max]
+        else:
+            sizes = [1 << k for k in range(10, 31) if (1 << k) <= args.sweep_max]
+        for size in sizes:
             s_sets, s_numel, _ = r.make_sets(size, dtype)
-            iters = 200 if size <= (1 << 20) else (50 if size <= (64 << 20) else 10)
-            t = r.time_steps(s_sets, args.op, 5, iters)
+            iters = 100 if size <= (1 << 20) else (20 if size <= (64 << 20) else 5)
+            t = median(r.time_steps(s_sets, args.op, 5, iters, 3)) / iters
             b = s_numel * s_sets[0][0].element_size()
-            sweep.append({"bytes": b, "time_us": round(t / iters * 1e6, 2), "busbw_gbs": round(busbw(b, t / iters, r.world), 2),
-                          "algo": (r.comm.last_call()["algo"] if r.comm is not None else args.impl)})
+            algo = r.comm.last_call()["algo"] if r.comm is not None else args.impl
+            row = {"bytes": b, "time_us": round(t * 1e6, 2), "busbw_gbs": round(busbw(b, t, r.world), 2), "algo": algo}
+            if r.world > 1 and r.comm is not None:
+                row["link_fraction_of_900"] = round(link_bytes_per_direction(algo, b, r.world) / t / 900e9, 3)
+            sweep.append(row)
+            r.release(s_sets)
             del s_sets
             torch.cuda.empty_cache()
-            size *= 2
 
     if r.rank == 0:
         per_step = seconds / args.steps
         value = busbw(nbytes, per_step, r.world)
         e2e_value = busbw(nbytes, e2e_seconds / e2e_steps, r.world)
+        algo = info.get("algo")
+        hbm_peak, peak_kind = measured_peaks()
         line = {
-            "metric": "allreduce_busbw_gbs_64MiB_float_sum" if r.world > 1 else "allreduce_algbw_gbs_64MiB_float_sum_single_gpu",
+            "metric": "allreduce_busbw_gbs_64MiB_float_sum",
             "value": round(value, 2),
             "unit": "GB/s",
             "impl": args.impl,
@@ -289,6 +351,9 @@ def run_measured(args):
             "steps": args.steps,
             "warmup": max(args.warmup, 3),
             "ms_per_step": round(per_step * 1e3, 5),
+            "repeats": len(batches),
+            "ms_per_step_min": round(min(batches) / args.steps * 1e3, 5),
+            "ms_per_step_max": round(max(batches) / args.steps * 1e3, 5),
             "higher_is_better": True,
             "scaling": "weak",
             "vs_baseline": round(value / BASELINE_BUSBW, 2),
@@ -301,10 +366,12 @@ def run_measured(args):
                 "collective": "all_reduce", "redop": args.op, "bytes_per_rank": nbytes, "global_batch": nbytes * r.world,
                 "seq_len": numel, "parallelism": f"allreduce{r.world}",
                 "buffers": args.buffers if r.comm is not None else "torch.empty (NCCL in place)",
-                "algo": info.get("algo"), "grid": info.get("grid"),
-                "l2": f"rotating over {len(sets)} buffer sets, {working >> 20} MiB working set > 126 MB L2",
-                "busbw_formula": "bytes/time * 2(n-1)/n; at n=1 the factor is 0, so the single-GPU value is bytes/time of the local copy kernel",
-                "timing": "CUDA events around K back-to-back steps, max over ranks",
+                "algo": algo, "grid": info.get("grid"),
+                "process_model": "one process per GPU (torchrun), peer memory shared as exported allocations",
+                "l2": f"rotating over {len(sets_desc(nbytes))} buffer sets, {working >> 20} MiB working set > 126 MB L2",
+                "busbw_formula": "bytes/time * 2(n-1)/n for n > 1; one GPU has no bus, so at n = 1 the value is bytes/time of "
+                                 "the device-to-device copy the collective degenerates to (see hbm_fraction)",
+                "timing": f"CUDA events around each batch of K back-to-back steps, max over ranks; median of {len(batches)} batches",
             },
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -312,15 +379,26 @@ def run_measured(args):
                     "note": "each step: pinned-host -> device copy of the whole input, all_reduce via Communicator.all_reduce, device -> pinned-host read of the first 1024 result elements"},
             "gpu_launches": launches if r.comm is not None else 0,
         }
+        if r.world > 1:
+            per_dir = link_bytes_per_direction(algo, nbytes, r.world)
+            line["link_fraction_of_900"] = round(per_dir / per_step / 900e9, 3)
+            line["link_model"] = f"{algo}: {per_dir / nbytes:.3f} x message bytes leave and enter every GPU per step"
+        else:
+            line["hbm_fraction"] = round(2 * nbytes / per_step / 1e9 / hbm_peak, 3)
+            line["hbm_peak"] = f"{hbm_peak:.0f} GB/s copy bandwidth ({peak_kind}); the copy reads and writes the message once each"
         if sweep is not None:
             line["sweep"] = sweep
         print(json.dumps(line), flush=True)
     if r.comm is not None:
-        del sets
         r.comm.close()
     if r.world > 1:
         r.dist.barrier()
         r.dist.destroy_process_group()
+
+
+def sets_desc(nbytes):
+    per_set = 2 * nbytes
+    return range(int(min(8, max(1, -(-4 * L2_BYTES // per_set)))))
 
 
 # ---------------------------------------------------------------------------------------------
@@ -386,6 +464,21 @@ def reference_measure(binary, args, n):
     except subprocess.TimeoutExpired:
         stock = {"error": "did not finish within 600 s"}
     clocks = sampler.stop((t0, t1))
+    # The reference's published range, 256 KiB .. 64 MiB x4, through its stock benchmark (host clock).
+    sweep = None
+    if args.sweep != "none":
+        try:
+            proc = subprocess.run([binary, "--dtype", args.dtype, "--redop", args.op, "--transport", args.ref_transport,
+                                   "-b", "262144", "-e", "67108864", "-f", "4", "-w", "5", "-n", "20"],
+                                  capture_output=True, text=True, timeout=600)
+            sweep = []
+            for line in proc.stdout.splitlines():
+                parts = line.split()
+                if not line.startswith("#") and len(parts) >= 11 and parts[4].isdigit():
+                    sweep.append({"bytes": int(parts[4]), "time_us": float(parts[6]), "busbw_gbs": float(parts[8]),
+                                  "algo": "ring_simple", "timing": "host clock (stock benchmark)"})
+        except subprocess.TimeoutExpired:
+            sweep = None
     if e2e_row is None and (stock is None or "error" in stock):
         return {"impl": "reference", "unavailable": f"reference gave no result: {harness_note}; stock: {stock}"[:300]}
     if e2e_row is not None:
@@ -410,8 +503,10 @@ def reference_measure(binary, args, n):
                    "bytes_per_rank": args.bytes, "global_batch": args.bytes * n, "seq_len": args.bytes // 4,
                    "parallelism": f"allreduce{n}", "transport": transport, "requested_transport": args.ref_transport,
                    "build": f"unmodified reference, -DNANO_NCCL_NRANKS={n} -DNANO_NCCL_CUDA_ARCH=100, one process driving {n} GPUs",
+                   "process_model": f"one process, one host thread driving {n} GPUs (the reference's only single-host model)",
                    "timing": timing, "l2": "single buffer pair of 2 x 64 MiB per GPU (the reference's FIFO traffic adds to it)"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps * n, "stock_benchmark": stock, "harness_note": harness_note,
+        "sweep": sweep,
     }
 
 

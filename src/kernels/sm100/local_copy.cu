@@ -1,6 +1,7 @@
 // Single-rank collectives: a device-to-device copy at HBM speed.
 //
-// One persistent CTA per SM; one elected thread per CTA drives a ring of shared-memory tiles with
+// One persistent CTA per SM, launched as a programmatic dependent of the kernel before it; one
+// elected thread per CTA drives a ring of shared-memory tiles with
 // TMA bulk copies: global -> shared (completion on an mbarrier), then shared -> global (bulk
 // group). No other thread touches the data, so the copy costs no registers and no load/store
 // instructions, and a slot is refilled as soon as the store that drained it has read it.
@@ -21,8 +22,10 @@ namespace {
 
 using u64 = unsigned long long;
 
-constexpr int kStages = 6;
-constexpr unsigned kTile = 32768;
+// Four stages of 27 KiB: enough loads in flight per SM for HBM, and small enough that the CTAs of
+// the NEXT copy in the stream fit on the SM beside this one's (see the dependent launch below).
+constexpr int kStages = 4;
+constexpr unsigned kTile = 27648;
 constexpr unsigned kPolls = 1u << 20;  // bound on waiting for an own bulk copy
 
 struct CopyShared {
@@ -39,6 +42,12 @@ __global__ void __launch_bounds__(32) bulk_copy_kernel(const unsigned char* src,
     const u64 mine = (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x;  // tiles blockIdx.x, +grid, +2 grid, ...
     for (int s = 0; s < kStages; ++s) mbar_init(&sm.full[s], 1);
     mbar_fence_init();
+    // Programmatic dependent launch: the next kernel in the stream may be scheduled now, so that its
+    // launch latency overlaps this kernel; this kernel in turn touches global memory only after the
+    // kernel before it has completed and its writes are visible. Both are no-ops for a kernel that
+    // was not launched with the attribute.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     auto tile_offset = [&](u64 i) { return (blockIdx.x + i * (u64)gridDim.x) * (u64)kTile; };
     auto tile_bytes = [&](u64 i) {
@@ -103,9 +112,18 @@ cudaError_t launch_local_copy(const void* src, void* dst, unsigned long long byt
     // The attribute belongs to the current device's copy of the function.
     st = cudaFuncSetAttribute(bulk_copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(CopyShared));
     if (st != cudaSuccess) return st;
-    bulk_copy_kernel<<<grid, 32, sizeof(CopyShared), stream>>>(static_cast<const unsigned char*>(src),
-                                                               static_cast<unsigned char*>(dst), bytes, status);
-    return cudaGetLastError();
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid, 1, 1);
+    config.blockDim = dim3(32, 1, 1);
+    config.dynamicSmemBytes = sizeof(CopyShared);
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, bulk_copy_kernel, static_cast<const unsigned char*>(src), static_cast<unsigned char*>(dst),
+                              static_cast<u64>(bytes), status);
 }
 
 }  // namespace b200ccl::kernels

@@ -66,12 +66,15 @@ def test_two_shot_pack_widths_agree(ranks, dtype):
     try:
         numel = (1 << 20) + 96 // esz  # a multiple of 32 bytes that no rank count divides evenly into packs
         gen = torch.Generator(device="cuda").manual_seed(11)
-        raw_in = [torch.randn(numel + 64, device="cuda", generator=gen).to(dtype) for _ in range(ranks)]
+        data = [torch.randn(numel, device="cuda", generator=gen).to(dtype) for _ in range(ranks)]
+        raw_in = [torch.empty(numel + 64, device="cuda", dtype=dtype) for _ in range(ranks)]
         raw_out = [torch.full((numel + 64,), float("nan"), device="cuda", dtype=dtype) for _ in range(ranks)]
         results = {}
         for name, shift in (("aligned32", 0), ("aligned16", 16 // esz)):
             ins = [t[shift:shift + numel] for t in raw_in]
             outs = [t[shift:shift + numel] for t in raw_out]
+            for view, values in zip(ins, data):
+                view.copy_(values)  # the same values behind both alignments
             for op in ("sum", "max"):
                 comm.all_reduce(outs, ins, op=op)
                 torch.cuda.synchronize()
