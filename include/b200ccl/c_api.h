@@ -68,6 +68,13 @@ int b2_collective(b2_comm* comm, int collective, const void* const* send, void* 
                   void* const* streams, size_t count, int dtype, int redop, int allow_in_place);
 /* What the last call resolved to: algo, grid, block, staged_in, staged_out, vectorized, pack_bytes. */
 int b2_comm_last_call(const b2_comm* comm, int out[7]);
+/* Ring wiring of one local rank's channel: send_fifo, recv_fifo, send_tail, send_head, recv_tail,
+ * recv_head, send_base, recv_base. Fails until a ring collective has run. */
+int b2_comm_ring_channel(const b2_comm* comm, int local_rank, int channel, const void* out[8]);
+/* Where an address lives, from cudaPointerGetAttributes: out[0] = 0 unknown, 1 host (pinned or
+ * mapped), 2 device, 3 managed; out[1] = the device that owns it (for host memory: the device whose
+ * context registered it). */
+int b2_pointer_info(const void* ptr, int out[2]);
 
 /* Symmetric heap: `ptrs` receives one pointer per local rank. Collective over all processes. */
 int b2_comm_alloc_symmetric(b2_comm* comm, size_t bytes, void** ptrs);

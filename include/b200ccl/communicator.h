@@ -107,6 +107,10 @@ public:
     void unregister_buffers(const std::vector<void*>& ptrs);
 
     CallInfo last_call() const noexcept;
+    // Addresses that one local rank's ring channel is wired to, in the order send_fifo, recv_fifo,
+    // send_tail, send_head, recv_tail, recv_head, send_base, recv_base (for tests that check which
+    // GPU, or the host, owns each of them). Throws until a ring collective has run.
+    std::vector<const void*> ring_channel_pointers(int local_rank, int channel) const;
     std::string describe() const;  // topology + per-edge transport report, one line per item
 
 private:

@@ -24,7 +24,16 @@ class B2Config(ctypes.Structure):
 
 
 def lib_path():
-    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libb200ccl.so")
+    """libb200ccl.so beside this file. B200CCL_LIBRARY=check selects the checking variant
+    (libb200ccl_check.so: test-only socket fault hook and device-side index checks compiled in);
+    any other value is taken as a path."""
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib")
+    choice = os.environ.get("B200CCL_LIBRARY", "")
+    if choice == "check":
+        return os.path.join(here, "libb200ccl_check.so")
+    if choice:
+        return choice
+    return os.path.join(here, "libb200ccl.so")
 
 
 def load():
@@ -64,6 +73,8 @@ def load():
     lib.b2_comm_describe.restype = cs
     lib.b2_collective.argtypes = [vp, ci, ctypes.POINTER(vp), ctypes.POINTER(vp), ctypes.POINTER(vp), cs, ci, ci, ci]
     lib.b2_comm_last_call.argtypes = [vp, ctypes.POINTER(ci)]
+    lib.b2_comm_ring_channel.argtypes = [vp, ci, ci, ctypes.POINTER(vp)]
+    lib.b2_pointer_info.argtypes = [vp, ctypes.POINTER(ci)]
     lib.b2_comm_alloc_symmetric.argtypes = [vp, cs, ctypes.POINTER(vp)]
     lib.b2_comm_free_symmetric.argtypes = [vp, ctypes.POINTER(vp)]
     lib.b2_comm_register.argtypes = [vp, ctypes.POINTER(vp), cs]

@@ -113,6 +113,13 @@ class Communicator:
         return {"algo": _ALGO_NAMES[out[0]], "grid": out[1], "block": out[2], "staged_in": bool(out[3]),
                 "staged_out": bool(out[4]), "vectorized": bool(out[5]), "pack_bytes": out[6]}
 
+    def ring_channel(self, local_rank=0, channel=0):
+        """Addresses one local rank's ring channel is wired to (after a ring collective has run)."""
+        out = (ctypes.c_void_p * 8)()
+        _lib.check(self._lib.b2_comm_ring_channel(self._handle, int(local_rank), int(channel), out))
+        names = ("send_fifo", "recv_fifo", "send_tail", "send_head", "recv_tail", "recv_head", "send_base", "recv_base")
+        return {k: int(v or 0) for k, v in zip(names, out)}
+
     def check_async_error(self):
         _lib.check(self._lib.b2_comm_check_async_error(self._handle))
 

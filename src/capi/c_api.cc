@@ -3,6 +3,7 @@
 #include "b200ccl/bootstrap.h"
 #include "b200ccl/communicator.h"
 #include "kernels/sm100/selftest.h"
+#include "core/check.h"
 #include "sched/plan.h"
 #include "sim/ll_sim.h"
 #include "sim/ring_sim.h"
@@ -158,6 +159,22 @@ int b2_comm_last_call(const b2_comm* c, int out[7]) {
     out[5] = i.vectorized;
     out[6] = i.pack_bytes;
     return 0;
+}
+
+int b2_comm_ring_channel(const b2_comm* c, int local_rank, int channel, const void* out[8]) {
+    return guarded([&] {
+        const auto v = c->comm->ring_channel_pointers(local_rank, channel);
+        for (size_t i = 0; i < 8 && i < v.size(); ++i) out[i] = v[i];
+    });
+}
+
+int b2_pointer_info(const void* ptr, int out[2]) {
+    return guarded([&] {
+        cudaPointerAttributes attr;
+        B2_CUDA(cudaPointerGetAttributes(&attr, ptr));
+        out[0] = static_cast<int>(attr.type);
+        out[1] = attr.device;
+    });
 }
 
 int b2_comm_alloc_symmetric(b2_comm* c, size_t bytes, void** ptrs) {

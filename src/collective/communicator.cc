@@ -29,6 +29,7 @@
 #include "topo/topology.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <initializer_list>
 #include <sstream>
@@ -78,6 +79,11 @@ public:
     void unregister_buffers(const std::vector<void*>& ptrs);
     void release_window(const std::vector<void*>& ptrs, const char* what);
     CallInfo last_call() const noexcept { return last_; }
+    std::vector<const void*> ring_channel_pointers(int local_rank, int channel) const {
+        if (!ring_) throw std::runtime_error("ring_channel_pointers: no ring collective has run on this communicator yet");
+        const dev::RingChannelView v = ring_->channel_view(local_rank, channel);
+        return {v.send_fifo, v.recv_fifo, v.send_tail, v.send_head, v.recv_tail, v.recv_head, v.send_base, v.recv_base};
+    }
     std::string describe() const;
 
 private:
@@ -121,7 +127,11 @@ private:
     bool multiprocess_ = false;
     Bootstrap* bootstrap_ = nullptr;
     TransportKind requested_ = TransportKind::Auto;
+    // P2p: every local ring edge uses peer memory (and the direct algorithms are available); Shm:
+    // every edge uses host memory; Mixed: some of each; Socket / Rdma: as requested.
     TransportKind resolved_ = TransportKind::P2p;
+    bool peer_memory_ = false;                    // every pair of local GPUs can address each other: symmetric memory exists
+    std::vector<TransportKind> local_edge_kind_;  // per ring edge e -> e+1 (global numbering); meaningful for edges inside this process
     Algo forced_algo_ = Algo::Auto;
     unsigned long long timeout_ns_ = 0;
     std::size_t staging_half_ = 0;
@@ -225,18 +235,23 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
     topo_ = topo::discover(config.devices);
     resolve_transport();
     {
-        // Per-edge view of the ring: edges inside a process use peer memory (or host memory for
-        // shm); edges between processes use exported peer memory unless a network transport was
-        // asked for; a single process that asked for socket/rdma loops every edge through it.
+        // Per-edge view of the ring: edges inside a process use peer memory or host memory, decided
+        // edge by edge; edges between processes use exported peer memory unless a network transport
+        // was asked for; a single process that asked for socket/rdma loops every edge through it.
         const bool net = resolved_ == TransportKind::Socket || resolved_ == TransportKind::Rdma;
-        const TransportKind local_kind = resolved_ == TransportKind::Shm ? TransportKind::Shm : TransportKind::P2p;
-        ring_plan_ = sched::make_ring_transport_plan(layout_, local_kind, net ? resolved_ : TransportKind::P2p,
+        ring_plan_ = sched::make_ring_transport_plan(layout_, TransportKind::P2p, net ? resolved_ : TransportKind::P2p,
                                                      net && !multiprocess_);
+        if (!(net && !multiprocess_)) {
+            for (int e = 0; e < static_cast<int>(ring_plan_.edge_kinds.size()); ++e) {
+                const bool inside = layout_.owner_of(e) == layout_.owner_of((e + 1) % nranks_);
+                if (inside && local_edge_kind_[e] == TransportKind::Shm) ring_plan_.edge_kinds[e] = TransportKind::Shm;
+            }
+        }
     }
 
-    // Peer-mapped memory exists for every transport except SHM, whose point is to work
-    // without peer access (everything it shares lives in mapped host memory).
-    if (resolved_ != TransportKind::Shm) {
+    // Peer-mapped (symmetric) memory needs every pair of GPUs to address each other. Without it
+    // only the ring runs, over per-edge FIFOs in the receiver's memory or in mapped host memory.
+    if (peer_memory_) {
         mem::GroupDesc group;
         group.nranks = nranks_;
         group.bootstrap = bootstrap_;
@@ -263,26 +278,104 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
              transport_name(resolved_), nvls_available() ? "yes" : "no");
 }
 
+namespace {
+
+// "0-1,2-3" -> pairs; "0,2" -> single numbers. Test hooks only; malformed text is an error.
+std::vector<std::pair<int, int>> parse_pairs(const char* text, const char* what) {
+    std::vector<std::pair<int, int>> out;
+    if (text == nullptr) return out;
+    std::stringstream ss(text);
+    std::string item;
+    while (std::getline(ss, item, ',')) {
+        if (item.empty()) continue;
+        char* end = nullptr;
+        const long a = std::strtol(item.c_str(), &end, 10);
+        long b = a;
+        if (*end == '-') b = std::strtol(end + 1, &end, 10);
+        if (end == item.c_str() || *end != '\0' || a < 0 || b < 0)
+            throw std::invalid_argument(std::string(what) + ": cannot parse '" + item + "'");
+        out.emplace_back(static_cast<int>(a), static_cast<int>(b));
+    }
+    return out;
+}
+
+}  // namespace
+
+// Decides, per ring edge inside this process, between peer memory and host memory.
+// Parity: nano-nccl resolve_ring_transport (src/transport/p2p/p2p_topology.cu:191-233): `auto`
+// looks at each edge, `p2p` must hold on every edge or fail, `shm` is uniform. Its `auto` also
+// demands a direct GPU-to-GPU NVLink (:53-90) and so picks SHM behind an NVSwitch; here peer
+// access in both directions is enough.
 void Communicator::Impl::resolve_transport() {
     std::vector<int> devs;
     for (const auto& l : local_)
         if (std::find(devs.begin(), devs.end(), l.device) == devs.end()) devs.push_back(l.device);
-    auto peers_ok = [&](std::string* why) { return devs.size() < 2 || mem::enable_all_peer_access(devs, why); };
+    // B200CCL_NO_PEER_PAIRS=a-b[,c-d]: treat these device pairs as unable to address each other
+    // (exercises the mixed plan on a machine where every pair can).
+    const auto denied = parse_pairs(env::get("B200CCL_NO_PEER_PAIRS"), "B200CCL_NO_PEER_PAIRS");
+    auto pair_ok = [&](int a, int b, std::string* why) {
+        if (a == b) return true;
+        for (const auto& d : denied) {
+            if ((d.first == a && d.second == b) || (d.first == b && d.second == a)) {
+                if (why) *why = "device " + std::to_string(a) + " cannot access device " + std::to_string(b) + " (B200CCL_NO_PEER_PAIRS)";
+                return false;
+            }
+        }
+        int ab = 0, ba = 0;
+        B2_CUDA(cudaDeviceCanAccessPeer(&ab, a, b));
+        B2_CUDA(cudaDeviceCanAccessPeer(&ba, b, a));
+        if (!(ab && ba) && why) *why = "device " + std::to_string(ab ? b : a) + " cannot access device " + std::to_string(ab ? a : b);
+        return ab && ba;
+    };
     std::string why;
+    bool all_pairs = true;
+    for (int a : devs)
+        for (int b : devs)
+            if (a < b && !pair_ok(a, b, all_pairs ? &why : nullptr)) all_pairs = false;
+    auto device_of = [&](int grank) {
+        for (const auto& l : local_)
+            if (l.grank == grank) return l.device;
+        return -1;
+    };
+    local_edge_kind_.assign(static_cast<std::size_t>(std::max(nranks_, 1)), TransportKind::P2p);
+    auto edges_by_access = [&]() {
+        bool any_shm = false;
+        for (int e = 0; e < nranks_; ++e) {
+            const int a = device_of(e), b = device_of((e + 1) % nranks_);
+            if (a < 0 || b < 0) continue;  // an edge that leaves this process
+            if (!pair_ok(a, b, nullptr)) {
+                local_edge_kind_[e] = TransportKind::Shm;
+                any_shm = true;
+            }
+        }
+        return any_shm;
+    };
     switch (requested_) {
-        case TransportKind::Auto:
-            // Every pair that can reach each other (directly or through NVSwitch) uses peer
-            // memory. nano-nccl's auto test (p2p_topology.cu:53-90) accepts only a direct
-            // GPU-to-GPU NVLink and so would pick SHM on an NVSwitch machine.
-            resolved_ = peers_ok(&why) ? TransportKind::P2p : TransportKind::Shm;
-            if (resolved_ == TransportKind::Shm) log_info("auto transport: %s → shm ring", why.c_str());
+        case TransportKind::Auto: {
+            if (multiprocess_ && !all_pairs) throw std::runtime_error("transport auto between processes needs peer access among this process's GPUs: " + why);
+            bool any_shm = edges_by_access();
+            // B200CCL_SHM_EDGES=e[,e]: these ring edges use host memory although peer memory would do.
+            for (const auto& f : parse_pairs(env::get("B200CCL_SHM_EDGES"), "B200CCL_SHM_EDGES")) {
+                if (f.first >= nranks_) throw std::invalid_argument("B200CCL_SHM_EDGES: no ring edge " + std::to_string(f.first));
+                if (device_of(f.first) >= 0 && device_of((f.first + 1) % nranks_) >= 0) {
+                    local_edge_kind_[f.first] = TransportKind::Shm;
+                    any_shm = true;
+                }
+            }
+            bool any_p2p = false;
+            for (int e = 0; e < nranks_; ++e)
+                if (device_of(e) >= 0 && device_of((e + 1) % nranks_) >= 0 && local_edge_kind_[e] == TransportKind::P2p) any_p2p = true;
+            resolved_ = !any_shm ? TransportKind::P2p : (any_p2p ? TransportKind::Mixed : TransportKind::Shm);
+            if (any_shm) log_info("auto transport: %s ring edges use host memory%s%s", any_p2p ? "some" : "all", why.empty() ? "" : ": ", why.c_str());
             break;
+        }
         case TransportKind::P2p:
-            if (!peers_ok(&why)) throw std::runtime_error("transport p2p requested but " + why);
+            if (!all_pairs) throw std::runtime_error("transport p2p requested but " + why);
             resolved_ = TransportKind::P2p;
             break;
         case TransportKind::Shm:
             if (multiprocess_) throw std::invalid_argument("transport shm needs all ranks in one process");
+            local_edge_kind_.assign(local_edge_kind_.size(), TransportKind::Shm);
             resolved_ = TransportKind::Shm;
             break;
         case TransportKind::Socket:
@@ -291,11 +384,15 @@ void Communicator::Impl::resolve_transport() {
             // process: every ring edge loops through it (TCP on the loopback interface, or the
             // in-process verbs backend), which tests the whole path on one host. Edges inside a
             // process still need peer access for the FIFOs of local edges.
-            if (!peers_ok(&why)) throw std::runtime_error(std::string("transport ") + transport_name(requested_) + ": " + why);
+            if (!all_pairs) throw std::runtime_error(std::string("transport ") + transport_name(requested_) + ": " + why);
             resolved_ = requested_;
             break;
         default: throw std::invalid_argument("bad transport");
     }
+    // Symmetric memory (and with it every direct algorithm) needs all pairs.
+    peer_memory_ = all_pairs && resolved_ != TransportKind::Shm;
+    if (peer_memory_ && devs.size() >= 2 && !mem::enable_all_peer_access(devs, &why))
+        throw std::runtime_error("enabling peer access failed: " + why);
 }
 
 Communicator::Impl::~Impl() {
@@ -416,7 +513,7 @@ void Communicator::Impl::register_buffers(const std::vector<void*>& ptrs, std::s
     if (ptrs.size() != local_.size()) throw std::invalid_argument("register_buffers: one pointer per local rank");
     if (bytes == 0) throw std::invalid_argument("register_buffers: size must be positive");
     if (!multiprocess_) return;  // one process: every device buffer is already peer-addressable
-    if (resolved_ == TransportKind::Shm) throw std::runtime_error("register_buffers: not available with transport shm");
+    if (!alloc_) throw std::runtime_error("register_buffers: not available without peer-mapped memory (transport shm)");
     Window w;
     w.ipc = mem::IpcWindow::create(group_, ptrs, bytes);
     w.bytes = bytes;
@@ -592,7 +689,7 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
     shape.peers_write_output = direct_peer_pointers() || out_sym;
     shape.input_multicast = in_sym && windows_[in_loc[0].region].mc != nullptr;
     shape.output_multicast = out_sym && windows_[out_loc[0].region].mc != nullptr;
-    shape.ring_only = resolved_ != TransportKind::P2p;  // shm, socket, rdma: only the ring crosses those edges
+    shape.ring_only = resolved_ != TransportKind::P2p;  // shm, mixed, socket, rdma: only the ring crosses those edges
     shape.max_ctas = tuning_.max_ctas;
     shape.staging_multicast = alloc_ && alloc_->multicast_supported() && (!stage_ || stage_->multicast_ptr() != nullptr);
     sched::Plan plan = sched::make_plan(shape, forced_algo_, tuning_);
@@ -623,7 +720,7 @@ void Communicator::Impl::run(Collective collective, const CollectiveArgs& args) 
             rc.nranks = nranks_;
             rc.channels = channels_;
             rc.timeout_ns = timeout_ns_;
-            rc.use_host_fifo = resolved_ == TransportKind::Shm;
+            rc.edge_kinds = ring_plan_.edge_kinds;
             rc.loopback = loopback_;
             if (resolved_ == TransportKind::Socket || resolved_ == TransportKind::Rdma) rc.net_kind = resolved_;
             for (const auto& l : local_) rc.local.push_back({l.grank, l.device});
@@ -857,6 +954,12 @@ void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sch
             if (oneshot) a.out[local_[i].grank] = static_cast<char*>(args.recv_buffers[i]) + off;
             if (plan.stage_in) a.user_in = static_cast<const char*>(args.send_buffers[i]) + off;
             if (plan.stage_out) a.user_out = static_cast<char*>(args.recv_buffers[i]) + off;
+            a.in_extent = a.out_extent = len;  // what in[p] and out[p] address, in packs (checking builds compare against it)
+#if defined(B200CCL_DEBUG_BOUNDS)
+            // Test hook of the checking build: pretend the buffers are this many packs shorter, as a
+            // wrong length computation on the host would; the kernel must record it and skip the accesses.
+            a.in_extent -= std::min<std::size_t>(len, env::get_bytes("B200CCL_DEBUG_SHRINK_EXTENT", 0));
+#endif
             if (nvls) {
                 a.mc_in = plan.stage_in ? static_cast<const char*>(stage_->multicast_ptr())
                                         : static_cast<const char*>(windows_[(*in_win)[i].region].mc) + (*in_win)[i].offset + off;
@@ -898,6 +1001,8 @@ void Communicator::Impl::launch_reduce_scatter(const CollectiveArgs& args, const
                 else if (direct) a.in[p] = static_cast<const char*>(args.send_buffers[p]) + off;
             }
             a.out[local_[i].grank] = static_cast<char*>(args.recv_buffers[i]) + off;
+            a.in_extent = a.in_stride * static_cast<std::size_t>(nranks_ - 1) + len;
+            a.out_extent = len;
             if (plan.stage_in) a.user_in = static_cast<const char*>(args.send_buffers[i]) + off;
             if (nvls) a.mc_in = static_cast<const char*>(windows_[(*in_win)[i].region].mc) + (*in_win)[i].offset + off;
         }
@@ -996,6 +1101,9 @@ void Communicator::register_buffers(const std::vector<void*>& ptrs, std::size_t 
 void Communicator::unregister_buffers(const std::vector<void*>& ptrs) { impl_->unregister_buffers(ptrs); }
 void Communicator::free_symmetric(const std::vector<void*>& ptrs) { impl_->free_symmetric(ptrs); }
 CallInfo Communicator::last_call() const noexcept { return impl_->last_call(); }
+std::vector<const void*> Communicator::ring_channel_pointers(int local_rank, int channel) const {
+    return impl_->ring_channel_pointers(local_rank, channel);
+}
 std::string Communicator::describe() const { return impl_->describe(); }
 
 std::unique_ptr<Communicator> create_communicator(const CommunicatorConfig& config) {

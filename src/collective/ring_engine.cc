@@ -18,16 +18,20 @@ struct RingEngine::State {
     RingEngineConfig cfg;
     std::size_t fifo_bytes = ring::kDefaultFifoBytes;
     Bootstrap* bootstrap = nullptr;
-    // Peer-to-peer edges: every rank's incoming FIFOs (channels × fifo_bytes) in its own memory.
+    // Peer-to-peer edges with all-pairs symmetric memory: every rank's incoming FIFOs
+    // (channels × fifo_bytes) in its own memory, counters in the communicator's control blocks.
     std::unique_ptr<mem::SymmetricRegion> fifo_region;
     const mem::SymmetricRegion* ctrl = nullptr;
+    // Without symmetric memory: a private control block per local rank (its neighbours store into
+    // it through pairwise peer access) and, for a rank whose incoming edge is P2p, a plain device FIFO.
+    std::vector<DeviceBuffer<dev::ControlBlock>> own_ctrl;
+    std::vector<DeviceBuffer<unsigned char>> dev_fifo;
     // Host (SHM) edges: FIFO and counters of edge e, channel c at index e*channels + c.
     std::vector<MappedBuffer<unsigned char>> host_fifo;
     MappedU64Array host_counters;  // [(e*channels + c)*2 + {0 tail, 1 head}]
-    MappedU64Array host_base;      // [(rank*channels + c)*2 + {0 send, 1 recv}]
-    std::vector<DeviceBuffer<dev::ControlBlock>> own_ctrl;  // host mode: one private block per local rank
     // Network edges (socket / RDMA) of this process, by direction.
     std::unique_ptr<transport::NetEdgeSet> net;
+    std::vector<std::vector<dev::RingChannel>> wiring;   // per local rank: [channels], host copy
     std::vector<DeviceBuffer<dev::RingChannel>> tables;  // per local rank: [channels]
     MappedBuffer<dev::RingTurnaroundStats> stats;        // [local rank][channel], optional
 };
@@ -37,6 +41,16 @@ int local_index_of(const RingEngineConfig& cfg, int grank) {
     for (std::size_t i = 0; i < cfg.local.size(); ++i)
         if (cfg.local[i].global_rank == grank) return static_cast<int>(i);
     return -1;
+}
+
+void enable_pair(int a, int b) {
+    if (a == b) return;
+    for (int k = 0; k < 2; ++k) {
+        DeviceGuard guard(k == 0 ? a : b);
+        const cudaError_t st = cudaDeviceEnablePeerAccess(k == 0 ? b : a, 0);
+        if (st == cudaErrorPeerAccessAlreadyEnabled) (void)cudaGetLastError();
+        else B2_CUDA(st);
+    }
 }
 }  // namespace
 
@@ -50,31 +64,51 @@ RingEngine::RingEngine(const RingEngineConfig& config, mem::SymmetricAllocator* 
     const int n = config.nranks, C = config.channels;
     if (n < 2) throw std::invalid_argument("ring needs at least two ranks");
     if (C < 1 || C > dev::kRingMaxChannels) throw std::invalid_argument("ring channel count out of range");
+    if (s.cfg.edge_kinds.empty()) s.cfg.edge_kinds.assign(n, TransportKind::P2p);
+    if (static_cast<int>(s.cfg.edge_kinds.size()) != n) throw std::invalid_argument("ring needs one transport kind per edge");
     s.fifo_bytes = env::get_bytes("B200CCL_FIFO_BUFF_BYTES", ring::kDefaultFifoBytes, "NANO_NCCL_FIFO_BUFF_BYTES");
     const std::size_t quantum = ring::kFifoSteps * ring::kGrainBytes;
     if (s.fifo_bytes < quantum || s.fifo_bytes % quantum != 0)
         throw std::invalid_argument("FIFO size must be a positive multiple of " + std::to_string(quantum) + " bytes");
 
-    const bool host = config.use_host_fifo;
     const bool net = config.net_kind != TransportKind::Auto;
-    if (!host) {
-        if (!alloc || !ctrl) throw std::invalid_argument("peer-to-peer ring needs symmetric memory");
-        s.fifo_region = alloc->allocate(static_cast<std::size_t>(C) * s.fifo_bytes, "ring-fifo");
+    const bool symmetric = alloc != nullptr && ctrl != nullptr;
+    auto is_shm = [&](int e) { return s.cfg.edge_kinds[e] == TransportKind::Shm; };
+    bool any_shm = false, any_p2p = false;
+    for (int e = 0; e < n; ++e) (is_shm(e) ? any_shm : any_p2p) = true;
+    if (!symmetric && (bootstrap != nullptr || net))
+        throw std::invalid_argument("a ring that leaves this process needs peer-mapped memory");
+
+    if (symmetric) {
+        // Every rank's incoming FIFOs in one symmetric region (unused by a rank whose incoming edge is SHM).
+        if (any_p2p || net) s.fifo_region = alloc->allocate(static_cast<std::size_t>(C) * s.fifo_bytes, "ring-fifo");
     } else {
+        for (const auto& l : config.local) {
+            s.own_ctrl.emplace_back(l.device, 1);
+            s.own_ctrl.back().zero();
+        }
+        s.dev_fifo.resize(config.local.size());
+        for (int e = 0; e < n; ++e) {
+            if (is_shm(e)) continue;
+            // P2p edge e -> e+1 without symmetric memory: FIFO on the receiver (p2p_fifo.cu:123-125 of
+            // the reference), peer access for this pair only (p2p_topology.cu:247-262).
+            const int src = local_index_of(config, e), dst = local_index_of(config, (e + 1) % n);
+            if (src < 0 || dst < 0) throw std::invalid_argument("ring edge without a local endpoint");
+            if (!config.loopback) enable_pair(config.local[src].device, config.local[dst].device);
+            s.dev_fifo[dst].reset(config.local[dst].device, static_cast<std::size_t>(C) * s.fifo_bytes);
+        }
+    }
+    if (any_shm) {
         // SHM: one FIFO per edge and channel in mapped host memory on the RECEIVER's NUMA node
-        // (nano-nccl communicator.cu:915-934), counters and base steps in mapped host memory too.
+        // (nano-nccl communicator.cu:915-934); its two counters in mapped host memory too.
         s.host_fifo.resize(static_cast<std::size_t>(n) * C);
         for (int e = 0; e < n; ++e) {
+            if (!is_shm(e)) continue;
             const int dst_local = local_index_of(config, (e + 1) % n);
             const int node = dst_local >= 0 ? numa::gpu_node(config.local[dst_local].device) : -1;
             for (int c = 0; c < C; ++c) s.host_fifo[e * C + c].reset(s.fifo_bytes, node);
         }
         s.host_counters.reset(static_cast<std::size_t>(n) * C * 2);
-        s.host_base.reset(static_cast<std::size_t>(n) * C * 2);
-        for (const auto& l : config.local) {
-            s.own_ctrl.emplace_back(l.device, 1);
-            s.own_ctrl.back().zero();
-        }
     }
     if (net) {
         transport::NetEdgeConfig nc;
@@ -88,37 +122,46 @@ RingEngine::RingEngine(const RingEngineConfig& config, mem::SymmetricAllocator* 
     }
     if (env::get_bool("B200CCL_RING_TURNAROUND", false)) s.stats.reset(config.local.size() * C);
 
-    // Wire every local rank's channel table.
+    auto ctrl_of = [&](int grank) -> dev::ControlBlock* {
+        if (symmetric) return static_cast<dev::ControlBlock*>(ctrl->rank_ptr(grank));
+        return s.own_ctrl[local_index_of(config, grank)].get();
+    };
+    auto fifo_of = [&](int grank, int c) -> char* {
+        char* base = symmetric ? static_cast<char*>(s.fifo_region->rank_ptr(grank))
+                               : reinterpret_cast<char*>(s.dev_fifo[local_index_of(config, grank)].get());
+        return base + static_cast<std::size_t>(c) * s.fifo_bytes;
+    };
+
+    // Wire every local rank's channel table, edge by edge.
     for (std::size_t i = 0; i < config.local.size(); ++i) {
         const int r = config.local[i].global_rank;
         const int next = (r + 1) % n, prev = (r + n - 1) % n;
+        const int out_e = r, in_e = prev;  // edge e goes e → e+1
         std::vector<dev::RingChannel> table(C);
         for (int c = 0; c < C; ++c) {
             dev::RingChannel ch;
             std::memset(&ch, 0, sizeof(ch));
-            if (host) {
-                const int out_e = r, in_e = prev;  // edge e goes e → e+1
+            dev::ControlBlock* mine = ctrl_of(r);
+            if (is_shm(out_e)) {
                 ch.send_fifo = s.host_fifo[out_e * C + c].get();
-                ch.recv_fifo = s.host_fifo[in_e * C + c].get();
                 ch.send_tail = &s.host_counters[(out_e * C + c) * 2 + 0];
                 ch.send_head = &s.host_counters[(out_e * C + c) * 2 + 1];
+            } else if (!s.net || s.net->send_half(r, c) == nullptr) {
+                ch.send_fifo = fifo_of(next, c);
+                ch.send_tail = &ctrl_of(next)->ring_recv_tail[c];  // publish into the next rank
+                ch.send_head = &mine->ring_send_head[c];           // poll locally
+            }
+            if (is_shm(in_e)) {
+                ch.recv_fifo = s.host_fifo[in_e * C + c].get();
                 ch.recv_tail = &s.host_counters[(in_e * C + c) * 2 + 0];
                 ch.recv_head = &s.host_counters[(in_e * C + c) * 2 + 1];
-                ch.send_base = &s.host_base[(r * C + c) * 2 + 0];
-                ch.recv_base = &s.host_base[(r * C + c) * 2 + 1];
-            } else {
-                auto* mine = static_cast<dev::ControlBlock*>(ctrl->rank_ptr(r));
-                auto* nxt = static_cast<dev::ControlBlock*>(ctrl->rank_ptr(next));
-                auto* prv = static_cast<dev::ControlBlock*>(ctrl->rank_ptr(prev));
-                ch.send_fifo = static_cast<char*>(s.fifo_region->rank_ptr(next)) + static_cast<std::size_t>(c) * s.fifo_bytes;
-                ch.recv_fifo = static_cast<char*>(s.fifo_region->rank_ptr(r)) + static_cast<std::size_t>(c) * s.fifo_bytes;
-                ch.send_tail = &nxt->ring_recv_tail[c];  // publish into the next rank
-                ch.send_head = &mine->ring_send_head[c];  // poll locally
-                ch.recv_tail = &mine->ring_recv_tail[c];  // poll locally
-                ch.recv_head = &prv->ring_send_head[c];   // publish into the previous rank
-                ch.send_base = &mine->ring_send_base[c];
-                ch.recv_base = &mine->ring_recv_base[c];
+            } else if (!s.net || s.net->recv_half(r, c) == nullptr) {
+                ch.recv_fifo = fifo_of(r, c);
+                ch.recv_tail = &mine->ring_recv_tail[c];               // poll locally
+                ch.recv_head = &ctrl_of(prev)->ring_send_head[c];      // publish into the previous rank
             }
+            ch.send_base = &mine->ring_send_base[c];
+            ch.recv_base = &mine->ring_recv_base[c];
             if (s.net) {
                 // Edges that leave this process go through host FIFOs served by proxy threads.
                 if (const transport::NetHalf* h = s.net->send_half(r, c)) {
@@ -141,11 +184,29 @@ RingEngine::RingEngine(const RingEngineConfig& config, mem::SymmetricAllocator* 
         s.tables.emplace_back(config.local[i].device, static_cast<std::size_t>(C));
         DeviceGuard guard(config.local[i].device);
         B2_CUDA(cudaMemcpy(s.tables.back().get(), table.data(), sizeof(dev::RingChannel) * C, cudaMemcpyHostToDevice));
+        s.wiring.push_back(std::move(table));
     }
     if (s.net) s.net->start();
     if (bootstrap) bootstrap->barrier();
-    log_info("ring engine: %d channels, %zu-byte FIFOs, %s edges%s", C, s.fifo_bytes, host ? "host" : "peer-to-peer",
-             s.net ? " + network edges" : "");
+    log_info("ring engine: %d channels, %zu-byte FIFOs, edges:%s%s%s", C, s.fifo_bytes, any_p2p ? " peer-to-peer" : "",
+             any_shm ? " host" : "", s.net ? " network" : "");
+}
+
+dev::RingChannelView RingEngine::channel_view(int local_index, int channel) const {
+    const State& s = *state_;
+    if (local_index < 0 || local_index >= static_cast<int>(s.wiring.size()) || channel < 0 || channel >= s.cfg.channels)
+        throw std::invalid_argument("ring channel view: index out of range");
+    const dev::RingChannel& ch = s.wiring[local_index][channel];
+    dev::RingChannelView v;
+    v.send_fifo = ch.send_fifo;
+    v.recv_fifo = ch.recv_fifo;
+    v.send_tail = ch.send_tail;
+    v.send_head = ch.send_head;
+    v.recv_tail = ch.recv_tail;
+    v.recv_head = ch.recv_head;
+    v.send_base = ch.send_base;
+    v.recv_base = ch.recv_base;
+    return v;
 }
 
 RingEngine::~RingEngine() {
@@ -185,8 +246,8 @@ void RingEngine::launch(Collective collective, const CollectiveArgs& args) {
         a.input = args.send_buffers[i];
         a.output = args.recv_buffers[i];
         a.channels = s.tables[i].get();
-        a.own_ctrl = s.cfg.use_host_fifo ? s.own_ctrl[i].get()
-                                         : static_cast<dev::ControlBlock*>(s.ctrl->rank_ptr(s.cfg.local[i].global_rank));
+        a.own_ctrl = s.ctrl != nullptr ? static_cast<dev::ControlBlock*>(s.ctrl->rank_ptr(s.cfg.local[i].global_rank))
+                                       : s.own_ctrl[i].get();
         a.status = s.cfg.status[i];
         a.count = args.count;
         a.step_elems = ring::step_elems(s.fifo_bytes, esz);

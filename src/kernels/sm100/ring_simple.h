@@ -39,6 +39,18 @@ struct RingChannel {
     RingTurnaroundStats* stats;     // optional
 };
 
+// The addresses of one channel's eight words and FIFOs, for inspection by tests.
+struct RingChannelView {
+    const void* send_fifo;
+    const void* recv_fifo;
+    const void* send_tail;
+    const void* send_head;
+    const void* recv_tail;
+    const void* recv_head;
+    const void* send_base;
+    const void* recv_base;
+};
+
 struct RingArgs {
     const void* input;
     void* output;

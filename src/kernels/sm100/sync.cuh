@@ -47,7 +47,10 @@ __device__ __forceinline__ void report_failure(Status* status, ControlBlock* own
                                                int nranks, unsigned int code, unsigned int peer,
                                                unsigned int where, unsigned long long epoch,
                                                unsigned long long waited_ns) {
-    if (status != nullptr && own != nullptr && atomicCAS(&own->fail_once, 0u, 1u) == 0u) {
+    // The first failure of a rank is the one recorded; a plan mismatch also replaces an earlier
+    // "aborted" record, which is only its echo from another CTA.
+    if (status != nullptr && own != nullptr &&
+        (atomicCAS(&own->fail_once, 0u, 1u) == 0u || (code == kStatusPlanMismatch && status->code != kStatusPlanMismatch))) {
         status->cta = blockIdx.x;
         status->peer = peer;
         status->where = where;

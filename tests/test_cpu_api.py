@@ -66,7 +66,13 @@ def test_planner_low_latency(lib, monkeypatch):
     WIDE, RD, WR, WORD = 1, 2, 4, 128
     monkeypatch.delenv("B200CCL_LL_MAX_BYTES", raising=False)
     rc, p = _plan(lib, 0, 1024, WIDE | RD | WR | WORD)
-    assert rc == 0 and p[0] == 1  # off unless asked for
+    assert rc == 0 and p[0] == 5  # small messages: no barrier at all
+    rc, p = _plan(lib, 0, 8192 + 4, WIDE | RD | WR | WORD)
+    assert rc == 0 and p[0] != 5  # above 32 KiB: the usual choice
+    monkeypatch.setenv("B200CCL_LL_MAX_BYTES", "0")
+    rc, p = _plan(lib, 0, 1024, WIDE | RD | WR | WORD)
+    assert rc == 0 and p[0] == 1  # switched off: one-shot
+    monkeypatch.delenv("B200CCL_LL_MAX_BYTES")
     rc, p = _plan(lib, 0, 1024, WORD, forced=5)
     assert rc == 0 and p[0] == 5 and p[1] == 8 and p[2] == 0 and p[3] == 0  # no staging even for private buffers
     rc, p = _plan(lib, 0, 32768, WORD, forced=5)
