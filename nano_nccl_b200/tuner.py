@@ -34,6 +34,9 @@ def parse_args():
     ap.add_argument("--algos", default="oneshot,twoshot,nvls",
                     help="comma list of oneshot,twoshot,nvls,ring,ll (ll: all_reduce up to 128 KiB, one CTA count)")
     ap.add_argument("--ctas", default="16,32,64,128")
+    ap.add_argument("--unrolls", default="", help="comma list of multimem loads in flight per thread (2,4,8) to try for nvls")
+    ap.add_argument("--sizes", default="", help="comma list of message sizes in bytes (default: every power of two in range)")
+    ap.add_argument("--iters", type=int, default=0, help="calls per timed batch (default: by size)")
     ap.add_argument("--graph", action="store_true", help="replay each batch from a CUDA graph")
     ap.add_argument("--emit-tuning", default="", help="also write the crossovers as a tuning file (B200CCL_TUNING_FILE)")
     ap.add_argument("--buffers", default="symmetric", choices=["symmetric", "plain"])
@@ -93,8 +96,10 @@ def main():
     rows = []
     algos = ["nccl"] if args.impl == "nccl" else args.algos.split(",")
     cta_list = [0] if args.impl == "nccl" else [int(c) for c in args.ctas.split(",")]
-    for algo in algos:
-        for ctas in cta_list:
+    unrolls = [int(u) for u in args.unrolls.split(",")] if args.unrolls else [0]
+    size_list = [int(s) for s in args.sizes.split(",")] if args.sizes else None
+    for algo, ctas, unroll in [(a, c, u) for a in algos for c in cta_list for u in (unrolls if a == "nvls" else [0])]:
+        if True:
             if args.impl == "nccl":
                 comm = NcclComm()
                 yield_comm = True
@@ -102,6 +107,8 @@ def main():
                 yield_comm = False
             if not yield_comm:
                 os.environ["B200CCL_MAX_CTAS"] = str(ctas)
+                if unroll:
+                    os.environ["B200CCL_NVLS_UNROLL"] = str(unroll)
                 port = [0]
                 if rank == 0:
                     s = socket.socket(); s.bind(("127.0.0.1", 0)); port[0] = s.getsockname()[1]; s.close()
@@ -111,8 +118,8 @@ def main():
                 if algo == "nvls" and not comm.nvls:
                     comm.close()
                     continue
-            size = args.min_bytes
-            while size <= args.max_bytes:
+            sizes = size_list if size_list is not None else [args.min_bytes << k for k in range(64) if (args.min_bytes << k) <= args.max_bytes]
+            for size in sizes:
                 if algo == "oneshot" and size > (8 << 20):
                     break
                 if algo == "ll" and (size > (128 << 10) or args.collective != "all_reduce" or ctas != cta_list[0]):
@@ -139,7 +146,7 @@ def main():
                         else:
                             comm.all_gather(y, x)
 
-                    iters = 200 if size <= (1 << 20) else (40 if size <= (64 << 20) else 8)
+                    iters = args.iters or (200 if size <= (1 << 20) else (40 if size <= (64 << 20) else 8))
                     for i in range(5):
                         call(i)
                     barrier()
@@ -166,7 +173,7 @@ def main():
                     info = comm.last_call()
                     total = numel * esize * (1 if args.collective == "all_reduce" else world)
                     factor = (2 * (world - 1) / world if args.collective == "all_reduce" else (world - 1) / world) if world > 1 else 1.0
-                    rows.append({"collective": args.collective, "algo": info["algo"], "requested": algo, "max_ctas": ctas,
+                    rows.append({"collective": args.collective, "algo": info["algo"], "requested": algo, "max_ctas": ctas, "unroll": unroll,
                                  "grid": info["grid"], "bytes": numel * esize, "time_us": round(t * 1e6, 2),
                                  "busbw_gbs": round(total / t / 1e9 * factor, 2)})
                     del sets, graph
@@ -174,7 +181,6 @@ def main():
                     if rank == 0:
                         print(f"skip {algo} ctas={ctas} size={size}: {e}", file=sys.stderr)
                     break
-                size *= 2
             comm.close()
     if rank == 0:
         best = {}

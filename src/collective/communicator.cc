@@ -29,6 +29,7 @@
 #include "topo/topology.h"
 
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <initializer_list>
@@ -145,6 +146,7 @@ private:
     std::unique_ptr<mem::SymmetricRegion> ctrl_;
     std::unique_ptr<mem::SymmetricRegion> stage_;
     std::unique_ptr<mem::SymmetricRegion> pipe_flags_;  // dev::PipeFlags per rank, allocated with the arena
+    std::vector<dev::PipeStats*> pipe_stats_;           // per local rank, device memory (B200CCL_PIPELINE_STATS=1)
     std::unique_ptr<mem::SymmetricRegion> ll_area_;  // receive slots of the low-latency kernel (first use)
     // A window is a buffer that exists on every rank and that every rank can address: a symmetric
     // allocation (with a multicast alias where available) or a registered ordinary buffer.
@@ -264,6 +266,13 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
         // Allocation is collective (and clears memory, which synchronises the device), so what the
         // small-message path needs exists before the first call rather than inside it.
         if (nranks_ >= 2) ll_area_ = alloc_->allocate(kernels::ll_area_bytes(nranks_), "low-latency slots");
+        // Between processes any call may need the staging arena (ordinary tensors of another process
+        // cannot be addressed), and which call does is a per-rank fact: allocating it on first use
+        // would leave a rank that needs it waiting, inside a collective allocation, for ranks that do not.
+        if (multiprocess_ && nranks_ >= 2) {
+            stage_ = alloc_->allocate(staging_half_ * 2, "staging");
+            pipe_flags_ = alloc_->allocate(sizeof(dev::PipeFlags), "pipeline flags");
+        }
     }
 
     for (auto& l : local_) {
@@ -272,6 +281,17 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
                               cudaHostAllocMapped | cudaHostAllocPortable));
         std::memset(l.status, 0, sizeof(dev::Status));
         B2_CUDA(cudaEventCreateWithFlags(&l.done, cudaEventDisableTiming));
+    }
+    if (env::get_bool("B200CCL_PIPELINE_STATS", false)) {
+        for (auto& l : local_) {
+            DeviceGuard guard(l.device);
+            // Device memory, read back at destruction: atomics into mapped host memory cross PCIe one by
+            // one, and system-scope releases on the same SM wait behind them.
+            dev::PipeStats* st = nullptr;
+            B2_CUDA(cudaMalloc(reinterpret_cast<void**>(&st), sizeof(dev::PipeStats)));
+            B2_CUDA(cudaMemset(st, 0, sizeof(dev::PipeStats)));
+            pipe_stats_.push_back(st);
+        }
     }
     // (The ring engine, its FIFOs and any network edges are built on the first call that needs them.)
     log_info("communicator: %d ranks (%d local, first %d), transport %s, nvls %s", nranks_, nlocal, first,
@@ -407,6 +427,30 @@ Communicator::Impl::~Impl() {
             }
         }
     }
+    for (std::size_t i = 0; i < pipe_stats_.size(); ++i) {
+        dev::PipeStats t;
+        std::memset(&t, 0, sizeof(t));
+        {
+            DeviceGuard guard(local_[i].device);
+            if (cudaMemcpy(&t, pipe_stats_[i], sizeof(t), cudaMemcpyDeviceToHost) != cudaSuccess) (void)cudaGetLastError();
+        }
+        if (t.calls != 0) {
+            int khz = 0;  // the counters are SM cycles; convert with the SM clock the device reports
+            cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, local_[i].device);
+            const double ns_per_cycle = khz > 0 ? 1e6 / static_cast<double>(khz) : 1.0;
+            const double per_tile = ns_per_cycle * 1e-3 / static_cast<double>(t.tiles ? t.tiles : 1);
+            std::fprintf(stderr,
+                         "pipeline stats v1 rank=%d cta_calls=%llu tiles=%llu per-tile us: in_wait_slot=%.2f in_copy=%.2f red_wait=%.2f "
+                         "red_work=%.2f out_wait=%.2f out_copy=%.2f kernel_ms_total=%.3f\n",
+                         local_[i].grank, t.calls, t.tiles, t.in_wait_slot_ns * per_tile, t.in_copy_ns * per_tile,
+                         t.red_wait_ns * per_tile, t.red_work_ns * per_tile, t.out_wait_ns * per_tile, t.out_copy_ns * per_tile,
+                         t.kernel_ns * ns_per_cycle * 1e-6);
+        }
+        {
+            DeviceGuard guard(local_[i].device);
+            cudaFree(pipe_stats_[i]);
+        }
+    }
     ring_.reset();
     windows_.clear();
     pipe_flags_.reset();
@@ -420,6 +464,12 @@ Communicator::Impl::~Impl() {
 }
 
 void Communicator::Impl::check_async_error() const {
+    if (latched_.empty() && ring_) {
+        // The root cause first: a failed proxy raises the abort word, and the kernels that leave
+        // their waits because of it only record the echo ("aborted").
+        const std::string e = ring_->async_error();
+        if (!e.empty()) latched_ = e;
+    }
     if (latched_.empty()) {
         for (const auto& l : local_) {
             const volatile dev::Status* s = l.status;
@@ -442,10 +492,6 @@ void Communicator::Impl::check_async_error() const {
                 latched_ = os.str();
                 break;
             }
-        }
-        if (latched_.empty() && ring_) {
-            const std::string e = ring_->async_error();
-            if (!e.empty()) latched_ = e;
         }
     }
     if (!latched_.empty()) throw std::runtime_error(latched_);
@@ -865,6 +911,7 @@ void Communicator::Impl::launch_pipeline(const CollectiveArgs& args, const sched
             a.mc_out = static_cast<char*>(stage_->multicast_ptr()) + staging_half_;
         }
         a.status = local_[i].status;
+        a.stats = pipe_stats_.empty() ? nullptr : pipe_stats_[i];
         a.bytes = bytes;
         a.tile_bytes = tile;
         a.timeout_ns = timeout_ns_;

@@ -67,7 +67,7 @@ __device__ __forceinline__ bool wait_flags(const RingArgs& a, ChannelState& st, 
     if ((flags & kRecv) && threadIdx.x == 0) {
         const u64 t0 = st.ch.stats ? global_timer_ns() : 0;
         ok = wait_at_least(st.ch.recv_tail, st.recv_step + ring::kSliceSteps, a.own_ctrl, a.timeout_ns, a.status, nullptr,
-                           0, (unsigned)((a.rank + a.nranks - 1) % a.nranks), 10u) ? 1 : 0;
+                           0, (unsigned)((a.rank + a.nranks - 1) % a.nranks), 10u, st.ch.abort_word) ? 1 : 0;
         if (ok && st.ch.abort_word && ld_volatile_u32(st.ch.abort_word) != 0u) ok = 0;
         if (st.ch.stats) t_wait_recv += global_timer_ns() - t0;
     }
@@ -77,7 +77,7 @@ __device__ __forceinline__ bool wait_flags(const RingArgs& a, ChannelState& st, 
         const u64 want = st.send_step + ring::kSliceSteps >= (u64)ring::kFifoSteps
                              ? st.send_step + ring::kSliceSteps - ring::kFifoSteps : 0;
         ok = wait_at_least(st.ch.send_head, want, a.own_ctrl, a.timeout_ns, a.status, nullptr, 0,
-                           (unsigned)((a.rank + 1) % a.nranks), 11u) ? 1 : 0;
+                           (unsigned)((a.rank + 1) % a.nranks), 11u, st.ch.abort_word) ? 1 : 0;
         if (ok && st.ch.abort_word && ld_volatile_u32(st.ch.abort_word) != 0u) ok = 0;
         if (st.ch.stats) t_wait_send += global_timer_ns() - t0;
     }

@@ -42,7 +42,7 @@ constexpr int kThreads = 512;
 constexpr int kCopyWarps = 2;                               // warp 0 copies in, warp 1 copies out
 constexpr int kReduceThreads = kThreads - 32 * kCopyWarps;  // 448
 constexpr int kStages = 3;                                  // shared-memory stages per copy direction
-constexpr unsigned kChunk = 16384;                          // bytes per TMA bulk copy
+constexpr unsigned kChunk = 32768;                          // bytes per TMA bulk copy
 constexpr unsigned kPolls = 1u << 20;                       // bound on waiting for an own bulk copy
 
 struct CopyRing {
@@ -61,6 +61,10 @@ template <typename A>
 __device__ __forceinline__ const A& select_args(const A& one) { return one; }
 template <typename A>
 __device__ __forceinline__ const A& select_args(const LoopPack<A>& all) { return all.r[blockIdx.y]; }
+
+// Stage timing uses the SM's own cycle counter: %globaltimer is one chip-wide register whose reads
+// from many SMs at once queue up for microseconds each, which would distort what is measured.
+__device__ __forceinline__ u64 stage_clock() { return (u64)clock64(); }
 
 __device__ __forceinline__ void reducers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kReduceThreads) : "memory"); }
 
@@ -105,16 +109,21 @@ __device__ bool bulk_copy(CopyRing& ring, u64& done, const uchar* src, uchar* ds
     return ok;
 }
 
-template <typename T, typename Op, bool kNvls, int kU, typename ParamT>
-__global__ void __launch_bounds__(kThreads) pipeline_kernel(const __grid_constant__ ParamT param) {
+// kN: rank count the peer-load loop is unrolled for (0: any, decided at run time). kU: packs in
+// flight per thread and peer. The two copy rings take most of an SM's shared memory, so one CTA
+// runs per SM and its threads may use the whole register file.
+template <typename T, typename Op, bool kNvls, int kN, int kU, typename ParamT>
+__global__ void __launch_bounds__(kThreads, 1) pipeline_kernel(const __grid_constant__ ParamT param) {
     using P = Wide<T>;
     constexpr int kElems = P::kElems;
+    constexpr int NN = kN > 0 ? kN : kMaxRanks;
     extern __shared__ __align__(128) uchar smem_raw[];
     Shared& sm = *reinterpret_cast<Shared*>(smem_raw);
     __shared__ u64 s_epoch, s_base;
 
     const PipeArgs& a = select_args(param);
-    const int n = a.nranks, rank = a.rank;
+    const int n = (kN > 0 && !kNvls) ? kN : a.nranks;
+    const int rank = a.rank;
     const unsigned cta = blockIdx.x;
     ControlBlock* own = a.ctrl[rank];
     PipeFlags* mine = a.flags[rank];
@@ -132,6 +141,7 @@ __global__ void __launch_bounds__(kThreads) pipeline_kernel(const __grid_constan
     __syncthreads();
     const u64 epoch = s_epoch + 1;
     const u64 base = s_base;
+    const u64 t_kernel = a.stats != nullptr ? stage_clock() : 0;
 
     // Every rank is inside this call (so nobody still uses the arena for an earlier one) and
     // launched it with the same plan.
@@ -149,53 +159,75 @@ __global__ void __launch_bounds__(kThreads) pipeline_kernel(const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     bool ok = true;
+    const bool timed = a.stats != nullptr;
 
     if (warp == 0) {
         // ---- copy-in: caller's input -> own arena ----------------------------------------------
         u64 chunks = 0;
         const uchar* src = static_cast<const uchar*>(a.user_in);
         uchar* dst = static_cast<uchar*>(a.arena_in[rank]);
+        u64 t_wait = 0, t_copy = 0;
         for (u64 k = 0; k < K; ++k) {
             int good = 1;
+            const u64 t0 = (timed && lane == 0) ? stage_clock() : 0;
             // The slot held tile k - S: every rank must have finished reducing it.
             if (k >= S && lane < n)
                 good = wait_at_least(&mine->reduced[cta][lane], base + k - S + 1, own, a.timeout_ns, a.status, a.ctrl, n,
                                      (unsigned)lane, 51u) ? 1 : 0;
             if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+            const u64 t1 = (timed && lane == 0) ? stage_clock() : 0;
             if (lane == 0) {
                 fence_proxy_async();
                 good = bulk_copy(sm.in, chunks, src + tile_off(k), dst + slot_off(k), tile_len(k)) ? 1 : 0;
                 if (!good) report_failure(a.status, own, a.ctrl, n, kStatusTimeout, (unsigned)rank, 52u, base + k, 0ull);
                 fence_proxy_async();
+                if (timed) { t_wait += t1 - t0; t_copy += stage_clock() - t1; }
             }
             // (the vote also orders lane 0's completed copies before the other lanes' signals)
             if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
             if (lane < n) st_release_sys(&a.flags[lane]->in_ready[cta][rank], base + k + 1);
+        }
+        if (timed && lane == 0) {
+            atomicAdd(&a.stats->in_wait_slot_ns, t_wait);
+            atomicAdd(&a.stats->in_copy_ns, t_copy);
+            atomicAdd(&a.stats->tiles, K);
+            atomicAdd(&a.stats->calls, 1ull);
         }
     } else if (warp == 1) {
         // ---- copy-out: own arena -> caller's output ----------------------------------------------
         u64 chunks = 0;
         const uchar* src = static_cast<const uchar*>(a.arena_out[rank]);
         uchar* dst = static_cast<uchar*>(a.user_out);
+        u64 t_wait = 0, t_copy = 0;
         for (u64 k = 0; k < K; ++k) {
             int good = 1;
+            const u64 t0 = (timed && lane == 0) ? stage_clock() : 0;
             if (lane < n)
                 good = wait_at_least(&mine->reduced[cta][lane], base + k + 1, own, a.timeout_ns, a.status, a.ctrl, n,
                                      (unsigned)lane, 53u) ? 1 : 0;
             if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+            const u64 t1 = (timed && lane == 0) ? stage_clock() : 0;
             if (lane == 0) {
                 fence_proxy_async();
                 good = bulk_copy(sm.out, chunks, src + slot_off(k), dst + tile_off(k), tile_len(k)) ? 1 : 0;
                 if (!good) report_failure(a.status, own, a.ctrl, n, kStatusTimeout, (unsigned)rank, 56u, base + k, 0ull);
+                if (timed) { t_wait += t1 - t0; t_copy += stage_clock() - t1; }
             }
             if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
             if (lane < n) st_release_sys(&a.flags[lane]->drained[cta][rank], base + k + 1);
+        }
+        if (timed && lane == 0) {
+            atomicAdd(&a.stats->out_wait_ns, t_wait);
+            atomicAdd(&a.stats->out_copy_ns, t_copy);
         }
     } else {
         // ---- reduce: own shard of the tile, all ranks' arenas -> all ranks' arenas --------------------
         const u64 rt = threadIdx.x - 32 * kCopyWarps;
         const bool scaled = a.scale != 1.0f;
+        u64 t_wait = 0, t_work = 0;
+        const bool clock = timed && rt == 0;  // one reader: %globaltimer is a slow read that serialises
         for (u64 k = 0; k < K; ++k) {
+            const u64 t0 = clock ? stage_clock() : 0;
             if (warp == kCopyWarps) {
                 int good = 1;
                 if (lane < n)  // every rank's copy of tile k is in its arena
@@ -209,6 +241,7 @@ __global__ void __launch_bounds__(kThreads) pipeline_kernel(const __grid_constan
             }
             reducers_sync();
             if (!sm.reduce_ok) { ok = false; break; }
+            const u64 t1 = clock ? stage_clock() : 0;
             const u64 packs = tile_len(k) / 16;
             const u64 lo = packs * (u64)rank / (u64)n, hi = packs * (u64)(rank + 1) / (u64)n;
             const u64 s0 = slot_off(k) / 16;
@@ -240,13 +273,13 @@ __global__ void __launch_bounds__(kThreads) pipeline_kernel(const __grid_constan
                 }
             } else {
                 for (u64 j = lo + rt; j < hi; j += (u64)kReduceThreads * kU) {
-                    uint4 r[kU][kMaxRanks];
+                    uint4 r[kU][NN];
 #pragma unroll
                     for (int u = 0; u < kU; ++u) {
                         const u64 jj = j + (u64)u * kReduceThreads;
                         if (jj < hi) {
 #pragma unroll
-                            for (int p = 0; p < kMaxRanks; ++p)
+                            for (int p = 0; p < NN; ++p)
                                 if (p < n) r[u][p] = P::load(a.arena_in[p], s0 + jj);
                         }
                     }
@@ -257,7 +290,7 @@ __global__ void __launch_bounds__(kThreads) pipeline_kernel(const __grid_constan
                             float acc[kElems];  // fixed order 0..n-1: bit-identical results on every rank
                             P::unpack(r[u][0], acc);
 #pragma unroll
-                            for (int p = 1; p < kMaxRanks; ++p) {
+                            for (int p = 1; p < NN; ++p) {
                                 if (p < n) {
                                     float f[kElems];
                                     P::unpack(r[u][p], f);
@@ -271,7 +304,7 @@ __global__ void __launch_bounds__(kThreads) pipeline_kernel(const __grid_constan
                             }
                             const uint4 v = P::pack(acc);
 #pragma unroll
-                            for (int q = 0; q < kMaxRanks; ++q) {
+                            for (int q = 0; q < NN; ++q) {
                                 if (q < n) {
                                     int dstr = rank + q;  // start with the own copy, then spread over peers
                                     if (dstr >= n) dstr -= n;
@@ -284,6 +317,11 @@ __global__ void __launch_bounds__(kThreads) pipeline_kernel(const __grid_constan
             }
             reducers_sync();  // every reducer's stores happen-before the release below
             if (warp == kCopyWarps && lane < n) st_release_sys(&a.flags[lane]->reduced[cta][rank], base + k + 1);
+            if (clock) { t_wait += t1 - t0; t_work += stage_clock() - t1; }
+        }
+        if (clock) {
+            atomicAdd(&a.stats->red_wait_ns, t_wait);
+            atomicAdd(&a.stats->red_work_ns, t_work);
         }
     }
 
@@ -294,6 +332,7 @@ __global__ void __launch_bounds__(kThreads) pipeline_kernel(const __grid_constan
         own->epoch[cta] = epoch;
         mine->base[cta] = base + K;
     }
+    if (threadIdx.x == 0 && cta == 0 && a.stats != nullptr) atomicAdd(&a.stats->kernel_ns, stage_clock() - t_kernel);
 }
 
 template <typename KernelT, typename ParamT>
@@ -311,15 +350,26 @@ cudaError_t launch_kernel(KernelT kernel, const ParamT& param, const PipeLaunch&
     return cudaGetLastError();
 }
 
-template <typename T, typename Op>
-cudaError_t launch_peer(const PipeArgs* args, const PipeLaunch& cfg) {
+template <typename T, typename Op, int kN, int kU>
+cudaError_t launch_peer_n(const PipeArgs* args, const PipeLaunch& cfg) {
     if (cfg.loop_ranks > 0) {
         if (cfg.loop_ranks > kMaxRanks) return cudaErrorInvalidValue;
         LoopPack<PipeArgs> pack;
         for (int r = 0; r < cfg.loop_ranks; ++r) pack.r[r] = args[r];
-        return launch_kernel(pipeline_kernel<T, Op, false, 2, LoopPack<PipeArgs>>, pack, cfg);
+        return launch_kernel(pipeline_kernel<T, Op, false, kN, kU, LoopPack<PipeArgs>>, pack, cfg);
     }
-    return launch_kernel(pipeline_kernel<T, Op, false, 2, PipeArgs>, args[0], cfg);
+    return launch_kernel(pipeline_kernel<T, Op, false, kN, kU, PipeArgs>, args[0], cfg);
+}
+
+// Fewer ranks leave registers for more packs in flight per peer.
+template <typename T, typename Op>
+cudaError_t launch_peer(const PipeArgs* args, const PipeLaunch& cfg) {
+    switch (args[0].nranks) {
+        case 2: return launch_peer_n<T, Op, 2, 8>(args, cfg);
+        case 4: return launch_peer_n<T, Op, 4, 4>(args, cfg);
+        case 8: return launch_peer_n<T, Op, 8, 2>(args, cfg);
+        default: return launch_peer_n<T, Op, 0, 2>(args, cfg);
+    }
 }
 
 template <typename T>
@@ -327,9 +377,9 @@ cudaError_t launch_t(RedOp op, const PipeArgs* args, const PipeLaunch& cfg) {
     if (cfg.nvls) {
         if (cfg.loop_ranks > 0 || (op != RedOp::Sum && op != RedOp::Avg) || args[0].mc_in == nullptr || args[0].mc_out == nullptr)
             return cudaErrorInvalidValue;
-        // (Eight loads in flight per thread spill at the 64 registers that let two CTAs share an SM.)
-        if (cfg.nvls_unroll <= 2) return launch_kernel(pipeline_kernel<T, OpAdd, true, 2, PipeArgs>, args[0], cfg);
-        return launch_kernel(pipeline_kernel<T, OpAdd, true, 4, PipeArgs>, args[0], cfg);
+        if (cfg.nvls_unroll >= 8) return launch_kernel(pipeline_kernel<T, OpAdd, true, 0, 8, PipeArgs>, args[0], cfg);
+        if (cfg.nvls_unroll <= 2) return launch_kernel(pipeline_kernel<T, OpAdd, true, 0, 2, PipeArgs>, args[0], cfg);
+        return launch_kernel(pipeline_kernel<T, OpAdd, true, 0, 4, PipeArgs>, args[0], cfg);
     }
     switch (op) {
         case RedOp::Sum:

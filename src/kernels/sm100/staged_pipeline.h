@@ -19,6 +19,21 @@ struct PipeFlags {
     unsigned long long base[kMaxCtas];                 // local: tiles this CTA index finished in earlier calls
 };
 
+// Where the pipeline's time goes, summed over CTAs and calls by the leading lane of every stage,
+// in SM clock cycles (despite the field names). Filled only when a pointer is passed
+// (B200CCL_PIPELINE_STATS=1).
+struct PipeStats {
+    unsigned long long in_wait_slot_ns;   // copy-in: waiting for the arena slot to be free
+    unsigned long long in_copy_ns;        // copy-in: moving the tile
+    unsigned long long red_wait_ns;       // reduce: waiting for every rank's tile (and a free output slot)
+    unsigned long long red_work_ns;       // reduce: loads, arithmetic, stores
+    unsigned long long out_wait_ns;       // copy-out: waiting for every rank's shard
+    unsigned long long out_copy_ns;       // copy-out: moving the tile
+    unsigned long long tiles;             // tiles counted (per CTA and call)
+    unsigned long long calls;             // CTAs x calls
+    unsigned long long kernel_ns;         // whole kernel, CTA 0 only, summed over calls
+};
+
 struct PipeArgs {
     const void* user_in;   // this rank's input (its own memory, 16-byte aligned)
     void* user_out;        // this rank's output
@@ -29,6 +44,7 @@ struct PipeArgs {
     ControlBlock* ctrl[kMaxRanks];
     PipeFlags* flags[kMaxRanks];
     Status* status;
+    PipeStats* stats;      // optional
     unsigned long long bytes;       // message size, a multiple of 16
     unsigned long long tile_bytes;  // a multiple of 16; CTA b owns tiles b, b + grid, ...
     unsigned long long timeout_ns;

@@ -65,12 +65,14 @@ __device__ __forceinline__ void report_failure(Status* status, ControlBlock* own
     }
 }
 
-// Spins until *flag >= want. Returns false after `timeout_ns`, or when the local abort flag is
-// set; the caller must then leave the kernel. The clock is read once every 64 polls.
+// Spins until *flag >= want. Returns false after `timeout_ns`, or when the local abort flag (or
+// `net_abort`, the host word a failed network proxy raises) is set; the caller must then leave
+// the kernel. The clock and the abort words are read once every 64 polls.
 __device__ __forceinline__ bool wait_at_least(const unsigned long long* flag, unsigned long long want,
                                               ControlBlock* own, unsigned long long timeout_ns,
                                               Status* status, ControlBlock* const* ctrl, int nranks,
-                                              unsigned int peer, unsigned int where) {
+                                              unsigned int peer, unsigned int where,
+                                              const unsigned int* net_abort = nullptr) {
     const unsigned int* abort_flag = own != nullptr ? &own->abort_flag : nullptr;
     if (ld_acquire_sys(flag) >= want) return true;
     const unsigned long long t0 = global_timer_ns();
@@ -78,7 +80,8 @@ __device__ __forceinline__ bool wait_at_least(const unsigned long long* flag, un
     for (;;) {
         if (ld_acquire_sys(flag) >= want) return true;
         if ((++polls & 63u) == 0u) {
-            if (abort_flag != nullptr && ld_volatile_u32(abort_flag) != 0u) {
+            if ((abort_flag != nullptr && ld_volatile_u32(abort_flag) != 0u) ||
+                (net_abort != nullptr && ld_volatile_u32(net_abort) != 0u)) {
                 report_failure(status, own, nullptr, 0, kStatusAborted, peer, where, want, global_timer_ns() - t0);
                 return false;
             }

@@ -40,8 +40,9 @@ Tuning default_tuning() {
     //    against 7.5-10.7 us for one-shot (its two barrier round trips).
     t.ll_max_bytes = 32u << 10;
     t.pipeline_min_bytes = 1u << 20;
-    t.pipeline_tile_bytes = 256u << 10;
+    t.pipeline_tile_bytes = 448u << 10;
     t.pipeline_max_ctas = 64;
+    t.pipeline_peer_max_ctas = 128;
     return t;
 }
 
@@ -89,6 +90,7 @@ Tuning tuning_from_text(const std::string& text, const Tuning& base, const std::
         else if (key == "pipeline_min_bytes") t.pipeline_min_bytes = bytes;
         else if (key == "pipeline_tile_bytes") t.pipeline_tile_bytes = std::max<std::size_t>(bytes / 4096 * 4096, 32u << 10);
         else if (key == "pipeline_max_ctas") t.pipeline_max_ctas = std::max(as_int, 1);
+        else if (key == "pipeline_peer_max_ctas") t.pipeline_peer_max_ctas = std::max(as_int, 1);
         else throw std::invalid_argument(where + "unknown key '" + key + "'");
     }
     return t;
@@ -123,6 +125,7 @@ Tuning tuning_from_env() {
     t.pipeline_min_bytes = env::get_bytes("B200CCL_PIPELINE_MIN_BYTES", t.pipeline_min_bytes);
     t.pipeline_tile_bytes = std::max<std::size_t>(env::get_bytes("B200CCL_PIPELINE_TILE_BYTES", t.pipeline_tile_bytes) / 4096 * 4096, 32u << 10);
     t.pipeline_max_ctas = std::max(1, static_cast<int>(env::get_int("B200CCL_PIPELINE_MAX_CTAS", t.pipeline_max_ctas)));
+    t.pipeline_peer_max_ctas = std::max(1, static_cast<int>(env::get_int("B200CCL_PIPELINE_PEER_MAX_CTAS", t.pipeline_peer_max_ctas)));
     return t;
 }
 
@@ -233,12 +236,17 @@ Plan make_plan(const CallShape& s, Algo forced, const Tuning& t) {
         p.algo = Algo::Pipeline;
         p.stage_in = p.stage_out = true;
         p.pipe_nvls = s.staging_multicast && s.nranks >= 3 && (s.redop == RedOp::Sum || s.redop == RedOp::Avg);
-        const int grid_max = std::max(1, std::min(cap, t.pipeline_max_ctas));
-        std::size_t tile = std::max<std::size_t>(t.pipeline_tile_bytes, 32u << 10);
-        while (tile > (32u << 10) && bytes / tile < 2 * static_cast<std::size_t>(grid_max)) tile /= 2;
-        tile = tile / 4096 * 4096;
+        // The peer-load reduce stage needs more CTAs than the switch one to keep NVLink busy.
+        const int grid_max = std::max(1, std::min(cap, p.pipe_nvls ? t.pipeline_max_ctas : t.pipeline_peer_max_ctas));
+        const std::size_t min_tile = 32u << 10;
+        const std::size_t grid = std::max<std::size_t>(1, std::min<std::size_t>(static_cast<std::size_t>(grid_max), bytes / min_tile));
+        const std::size_t per_cta = (bytes + grid - 1) / grid;
+        // Every CTA gets the same number of tiles, each close to the preferred size.
+        const std::size_t target = std::max<std::size_t>(t.pipeline_tile_bytes, min_tile);
+        const std::size_t tiles_per_cta = std::max<std::size_t>(1, (per_cta + target / 2) / target);
+        const std::size_t tile = ((per_cta + tiles_per_cta - 1) / tiles_per_cta + 4095) / 4096 * 4096;
         p.tile_bytes = tile;
-        p.grid = static_cast<int>(std::min<std::size_t>(static_cast<std::size_t>(grid_max), (bytes + tile - 1) / tile));
+        p.grid = static_cast<int>(std::min<std::size_t>(grid, (bytes + tile - 1) / tile));
         return p;
     }
     Algo algo = forced;

@@ -63,11 +63,12 @@ struct Tuning {
     bool wide32 = true;
     // AllReduce of buffers that peers cannot address: from this size up the copy into the staging arena,
     // the reduction and the copy out run as a tile pipeline in one kernel (B200CCL_PIPELINE_MIN_BYTES;
-    // below it: copy, barrier, reduce, barrier, copy). Tiles of pipeline_tile_bytes, halved for small
-    // messages down to 32 KiB until every CTA has two; at most pipeline_max_ctas CTAs.
+    // below it: copy, barrier, reduce, barrier, copy). Every CTA gets the same number of tiles of about
+    // pipeline_tile_bytes (never under 32 KiB); at most pipeline_max_ctas CTAs.
     std::size_t pipeline_min_bytes = 0;
     std::size_t pipeline_tile_bytes = 0;
-    int pipeline_max_ctas = 64;
+    int pipeline_max_ctas = 64;        // reduce stage through the switch (multimem)
+    int pipeline_peer_max_ctas = 128;  // reduce stage over peer loads and stores
 };
 Tuning default_tuning();
 // default_tuning(), then the file named by B200CCL_TUNING_FILE (if set), then the B200CCL_* variables.
@@ -75,7 +76,7 @@ Tuning tuning_from_env();
 // Applies a tuning file to `base`. One `key = value` per line, `#` starts a comment; byte counts take
 // K/M/G suffixes. Keys: oneshot_max_bytes (all rank counts) or oneshot_max_bytes.<nranks>, nvls_min_bytes,
 // max_ctas, nvls_max_ctas, twoshot_max_ctas, nvls_unroll, bytes_per_cta, oneshot_bytes_per_cta, ll_max_bytes, wide32,
-// pipeline_min_bytes, pipeline_tile_bytes, pipeline_max_ctas.
+// pipeline_min_bytes, pipeline_tile_bytes, pipeline_max_ctas, pipeline_peer_max_ctas.
 // `python -m nano_nccl_b200.tuner --emit-tuning FILE` writes such a file from its measurements.
 // Throws std::invalid_argument naming the file and line on an unknown key or a bad value.
 Tuning tuning_from_text(const std::string& text, const Tuning& base, const std::string& origin);

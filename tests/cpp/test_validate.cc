@@ -96,7 +96,7 @@ int main() {
     s = sched::CallShape{}; s.nranks = 4; s.count = 1 << 20; s.wide = true;  // plain buffers of another process
     plan = sched::make_plan(s, Algo::Auto, sched::default_tuning());
     T_CHECK(plan.stage_in && plan.stage_out && plan.algo == Algo::Pipeline);  // 4 MiB: the tile pipeline
-    T_CHECK(plan.tile_bytes >= (32u << 10) && plan.tile_bytes % 4096 == 0 && plan.grid >= 1 && plan.grid <= 64);
+    T_CHECK(plan.tile_bytes >= (32u << 10) && plan.tile_bytes % 4096 == 0 && plan.grid >= 1 && plan.grid <= 128);
     T_CHECK((static_cast<std::size_t>(4) << 20) / plan.tile_bytes >= static_cast<std::size_t>(plan.grid));  // no CTA without a tile
     T_CHECK(!plan.pipe_nvls);                      // the arena has no multicast alias in this shape
     s.staging_multicast = true;
