@@ -91,7 +91,10 @@ class BucketAllReducer:
         for b in self.buckets:
             b.zero_()
         self.cuda = self.device.type == "cuda"
-        self.stream = torch.cuda.Stream(self.device) if self.cuda else None
+        # High priority: when the reduction is issued beside a stream of matmuls, its CTAs (which spin until
+        # the same CTAs of every rank are resident) are placed as soon as an SM frees up instead of after the
+        # matmul's whole grid.
+        self.stream = torch.cuda.Stream(self.device, priority=-1) if self.cuda else None
         self._ready = [torch.cuda.Event() for _ in self.buckets] if self.cuda else []
         self._done = [torch.cuda.Event() for _ in self.buckets] if self.cuda else []
         self.launches = 0

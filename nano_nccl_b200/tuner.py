@@ -106,7 +106,10 @@ def main():
             else:
                 yield_comm = False
             if not yield_comm:
-                os.environ["B200CCL_MAX_CTAS"] = str(ctas)
+                if ctas > 0:
+                    os.environ["B200CCL_MAX_CTAS"] = str(ctas)  # an explicit cap applies to every algorithm
+                else:
+                    os.environ.pop("B200CCL_MAX_CTAS", None)    # 0: the library's own per-algorithm caps
                 if unroll:
                     os.environ["B200CCL_NVLS_UNROLL"] = str(unroll)
                 port = [0]

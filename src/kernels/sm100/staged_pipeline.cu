@@ -68,47 +68,6 @@ __device__ __forceinline__ u64 stage_clock() { return (u64)clock64(); }
 
 __device__ __forceinline__ void reducers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kReduceThreads) : "memory"); }
 
-// Copies `bytes` from src to dst (both global, this GPU's own memory, 16-byte aligned, size a
-// multiple of 16) through the ring, driven by the calling thread alone. `done` counts the chunks
-// this ring has carried so far; it selects the stage and the mbarrier parity. Every stage is free
-// on entry and on return, and on return every store has completed. False: an own copy did not
-// land within the bound (copies still in flight were given a bounded time to land).
-__device__ bool bulk_copy(CopyRing& ring, u64& done, const uchar* src, uchar* dst, u64 bytes) {
-    const u64 n = (bytes + kChunk - 1) / kChunk;
-    auto chunk_bytes = [&](u64 i) {
-        const u64 off = i * kChunk;
-        return (unsigned)(bytes - off < kChunk ? bytes - off : kChunk);
-    };
-    auto load = [&](u64 i) {
-        const int s = (int)((done + i) % kStages);
-        mbar_arrive_expect_tx(&ring.full[s], chunk_bytes(i));
-        tma_load_bulk(ring.tile[s], src + i * kChunk, chunk_bytes(i), &ring.full[s]);
-    };
-    u64 loaded = n < (u64)kStages ? n : (u64)kStages;
-    for (u64 i = 0; i < loaded; ++i) load(i);
-    bool ok = true;
-    u64 i = 0;
-    for (; i < n; ++i) {
-        const u64 g = done + i;
-        const int s = (int)(g % kStages);
-        if (!mbar_wait_bounded(&ring.full[s], (unsigned)((g / kStages) & 1), kPolls)) {
-            ok = false;
-            break;
-        }
-        tma_store_bulk(dst + i * kChunk, ring.tile[s], chunk_bytes(i));
-        tma_commit_group();
-        if (i >= 1 && loaded < n) {
-            tma_wait_group_read<1>();  // the store before the newest has read its stage: refill it
-            load(loaded++);
-        }
-    }
-    if (!ok)
-        for (u64 k = i + 1; k < loaded; ++k) mbar_wait_bounded(&ring.full[(done + k) % kStages], (unsigned)(((done + k) / kStages) & 1), kPolls);
-    tma_wait_group_all();
-    done += n;
-    return ok;
-}
-
 // kN: rank count the peer-load loop is unrolled for (0: any, decided at run time). kU: packs in
 // flight per thread and peer. The two copy rings take most of an SM's shared memory, so one CTA
 // runs per SM and its threads may use the whole register file.
@@ -161,64 +120,132 @@ __global__ void __launch_bounds__(kThreads, 1) pipeline_kernel(const __grid_cons
     bool ok = true;
     const bool timed = a.stats != nullptr;
 
-    if (warp == 0) {
-        // ---- copy-in: caller's input -> own arena ----------------------------------------------
-        u64 chunks = 0;
-        const uchar* src = static_cast<const uchar*>(a.user_in);
-        uchar* dst = static_cast<uchar*>(a.arena_in[rank]);
-        u64 t_wait = 0, t_copy = 0;
-        for (u64 k = 0; k < K; ++k) {
-            int good = 1;
-            const u64 t0 = (timed && lane == 0) ? stage_clock() : 0;
-            // The slot held tile k - S: every rank must have finished reducing it.
-            if (k >= S && lane < n)
-                good = wait_at_least(&mine->reduced[cta][lane], base + k - S + 1, own, a.timeout_ns, a.status, a.ctrl, n,
-                                     (unsigned)lane, 51u) ? 1 : 0;
-            if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
-            const u64 t1 = (timed && lane == 0) ? stage_clock() : 0;
-            if (lane == 0) {
-                fence_proxy_async();
-                good = bulk_copy(sm.in, chunks, src + tile_off(k), dst + slot_off(k), tile_len(k)) ? 1 : 0;
-                if (!good) report_failure(a.status, own, a.ctrl, n, kStatusTimeout, (unsigned)rank, 52u, base + k, 0ull);
-                fence_proxy_async();
-                if (timed) { t_wait += t1 - t0; t_copy += stage_clock() - t1; }
+    if (warp <= 1) {
+        // ---- the two copy stages: one elected thread each, a continuous stream of chunks ------------
+        // Chunks flow through the shared-memory ring without a pause at tile borders: loads run up to
+        // kStages chunks ahead of stores, a stage is refilled once the store that drained it has read
+        // it, and a tile is announced as soon as the stores (copy-in) or loads (copy-out) of its last
+        // chunk are known to be complete.
+        if (lane == 0) {
+            const bool in = warp == 0;
+            CopyRing& ring = in ? sm.in : sm.out;
+            const uchar* src = in ? static_cast<const uchar*>(a.user_in) : static_cast<const uchar*>(a.arena_out[rank]);
+            uchar* dst = in ? static_cast<uchar*>(a.arena_in[rank]) : static_cast<uchar*>(a.user_out);
+            auto chunks_of = [&](u64 k) { return (tile_len(k) + kChunk - 1) / kChunk; };
+            auto chunk_len = [&](u64 k, u64 j) {
+                const u64 left = tile_len(k) - j * kChunk;
+                return (unsigned)(left < kChunk ? left : kChunk);
+            };
+            u64 total = 0;
+            for (u64 k = 0; k < K; ++k) total += chunks_of(k);
+            // A tile is announced to every rank with one fence and n relaxed stores (a release).
+            auto announce = [&](unsigned long long (PipeFlags::*row)[kMaxCtas][kMaxRanks], u64 tiles) {
+                fence_acq_rel_sys();
+                for (int p = 0; p < n; ++p) st_relaxed_sys(&(a.flags[p]->*row)[cta][rank], base + tiles);
+            };
+            auto wait_all = [&](unsigned long long (*row)[kMaxRanks], u64 want, unsigned where) {
+                for (int p = 0; p < n; ++p)
+                    if (!wait_at_least(&row[cta][p], want, own, a.timeout_ns, a.status, a.ctrl, n, (unsigned)p, where)) return false;
+                return true;
+            };
+            u64 lk = 0, lj = 0, issued = 0;       // next chunk to load
+            u64 sk = 0, sj = 0, stores = 0;        // next chunk to store
+            u64 freed = 0;                         // chunks whose store has finished reading its stage
+            u64 closed = 0;                        // tiles all of whose stores have been issued (copy-in) / loads have landed (copy-out)
+            u64 announced = 0;                     // tiles announced to the other ranks
+            u64 t_wait = 0, t_busy = 0, t_mark = timed ? stage_clock() : 0;
+            while (ok && stores < total) {
+                // 1. Loads, as far ahead as stages and the arena slots allow.
+                while (ok && issued < total && issued < freed + kStages) {
+                    if (lj == 0) {
+                        const u64 t0 = timed ? stage_clock() : 0;
+                        if (in) {
+                            if (lk >= S) {
+                                // The slot held tile lk - S: every rank must have reduced it, which needs this
+                                // rank's own copy of that tile to be announced first.
+                                const u64 need = lk - S + 1;
+                                if (closed < need) break;  // its stores are not even issued: store first
+                                if (announced < need) {
+                                    tma_wait_group_all();
+                                    freed = stores;
+                                    announce(&PipeFlags::in_ready, closed);
+                                    announced = closed;
+                                }
+                                ok = wait_all(mine->reduced, base + need, 51u);
+                            }
+                        } else {
+                            // Tile lk must have been reduced by every rank, which (from tile S on) needs this
+                            // rank to have announced that it drained tile lk - S.
+                            if (lk >= S && announced < lk - S + 1) break;
+                            ok = wait_all(mine->reduced, base + lk + 1, 53u);
+                            // Peers wrote the slot through the generic proxy; the bulk copies below read it
+                            // through the asynchronous one.
+                            fence_proxy_async();
+                        }
+                        if (timed) t_wait += stage_clock() - t0;
+                        if (!ok) break;
+                    }
+                    const int s = (int)(issued % kStages);
+                    const unsigned len = chunk_len(lk, lj);
+                    mbar_arrive_expect_tx(&ring.full[s], len);
+                    tma_load_bulk(ring.tile[s], src + (in ? tile_off(lk) : slot_off(lk)) + lj * kChunk, len, &ring.full[s]);
+                    ++issued;
+                    if (++lj == chunks_of(lk)) { ++lk; lj = 0; }
+                }
+                if (!ok) break;
+                // 2. The next chunk has landed: store it.
+                const int s = (int)(stores % kStages);
+                if (!mbar_wait_bounded(&ring.full[s], (unsigned)((stores / kStages) & 1), kPolls)) {
+                    report_failure(a.status, own, a.ctrl, n, kStatusTimeout, (unsigned)rank, in ? 52u : 56u, base + sk, 0ull);
+                    ok = false;
+                    break;
+                }
+                const bool last_of_tile = sj + 1 == chunks_of(sk);
+                if (!in && last_of_tile) {
+                    // Every load of the tile has landed in shared memory: its arena slot may be reused.
+                    ++closed;
+                    announce(&PipeFlags::drained, closed);
+                    announced = closed;
+                }
+                const u64 closed_before = closed;
+                tma_store_bulk(dst + (in ? slot_off(sk) : tile_off(sk)) + sj * kChunk, ring.tile[s], chunk_len(sk, sj));
+                tma_commit_group();
+                ++stores;
+                if (last_of_tile) {
+                    if (in) ++closed;
+                    ++sk;
+                    sj = 0;
+                } else {
+                    ++sj;
+                }
+                if (in && closed_before > announced) {
+                    // Tiles closed by an earlier store: complete once all groups but the newest are.
+                    tma_wait_group<1>();
+                    freed = stores - 1;
+                    announce(&PipeFlags::in_ready, closed_before);
+                    announced = closed_before;
+                } else if (stores >= 2) {
+                    tma_wait_group_read<1>();
+                    freed = stores - 1;
+                }
             }
-            // (the vote also orders lane 0's completed copies before the other lanes' signals)
-            if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
-            if (lane < n) st_release_sys(&a.flags[lane]->in_ready[cta][rank], base + k + 1);
-        }
-        if (timed && lane == 0) {
-            atomicAdd(&a.stats->in_wait_slot_ns, t_wait);
-            atomicAdd(&a.stats->in_copy_ns, t_copy);
-            atomicAdd(&a.stats->tiles, K);
-            atomicAdd(&a.stats->calls, 1ull);
-        }
-    } else if (warp == 1) {
-        // ---- copy-out: own arena -> caller's output ----------------------------------------------
-        u64 chunks = 0;
-        const uchar* src = static_cast<const uchar*>(a.arena_out[rank]);
-        uchar* dst = static_cast<uchar*>(a.user_out);
-        u64 t_wait = 0, t_copy = 0;
-        for (u64 k = 0; k < K; ++k) {
-            int good = 1;
-            const u64 t0 = (timed && lane == 0) ? stage_clock() : 0;
-            if (lane < n)
-                good = wait_at_least(&mine->reduced[cta][lane], base + k + 1, own, a.timeout_ns, a.status, a.ctrl, n,
-                                     (unsigned)lane, 53u) ? 1 : 0;
-            if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
-            const u64 t1 = (timed && lane == 0) ? stage_clock() : 0;
-            if (lane == 0) {
-                fence_proxy_async();
-                good = bulk_copy(sm.out, chunks, src + slot_off(k), dst + tile_off(k), tile_len(k)) ? 1 : 0;
-                if (!good) report_failure(a.status, own, a.ctrl, n, kStatusTimeout, (unsigned)rank, 56u, base + k, 0ull);
-                if (timed) { t_wait += t1 - t0; t_copy += stage_clock() - t1; }
+            // Stores read shared memory (and must be complete before the kernel's results count).
+            if (!ok)
+                for (u64 g = stores + 1; g < issued; ++g) mbar_wait_bounded(&ring.full[g % kStages], (unsigned)((g / kStages) & 1), kPolls);
+            tma_wait_group_all();
+            if (ok && in && announced < closed) announce(&PipeFlags::in_ready, closed);
+            if (timed) {
+                t_busy = stage_clock() - t_mark - t_wait;
+                if (in) {
+                    atomicAdd(&a.stats->in_wait_slot_ns, t_wait);
+                    atomicAdd(&a.stats->in_copy_ns, t_busy);
+                    atomicAdd(&a.stats->tiles, K);
+                    atomicAdd(&a.stats->calls, 1ull);
+                } else {
+                    atomicAdd(&a.stats->out_wait_ns, t_wait);
+                    atomicAdd(&a.stats->out_copy_ns, t_busy);
+                }
             }
-            if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
-            if (lane < n) st_release_sys(&a.flags[lane]->drained[cta][rank], base + k + 1);
-        }
-        if (timed && lane == 0) {
-            atomicAdd(&a.stats->out_wait_ns, t_wait);
-            atomicAdd(&a.stats->out_copy_ns, t_copy);
         }
     } else {
         // ---- reduce: own shard of the tile, all ranks' arenas -> all ranks' arenas --------------------

@@ -58,6 +58,11 @@ template <int kPending>
 __device__ __forceinline__ void tma_wait_group_read() {
     asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
 }
+// Waits until at most kPending of the thread's bulk groups have not COMPLETED (writes performed).
+template <int kPending>
+__device__ __forceinline__ void tma_wait_group() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(kPending) : "memory");
+}
 // Waits until every bulk group of the thread has completed (its writes are performed).
 __device__ __forceinline__ void tma_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Orders this thread's earlier generic-proxy accesses before later async-proxy (TMA) accesses.

@@ -40,7 +40,7 @@ Tuning default_tuning() {
     //    against 7.5-10.7 us for one-shot (its two barrier round trips).
     t.ll_max_bytes = 32u << 10;
     t.pipeline_min_bytes = 1u << 20;
-    t.pipeline_tile_bytes = 448u << 10;
+    t.pipeline_tile_bytes = 256u << 10;
     t.pipeline_max_ctas = 64;
     t.pipeline_peer_max_ctas = 128;
     return t;
