@@ -606,7 +606,7 @@ void Communicator::Impl::launch_reduce_ranks(const CollectiveArgs& args, std::ve
                                              int pack_bytes, bool nvls, int grid) {
     kernels::LaunchConfig cfg;
     cfg.grid = std::min(grid, dev::kMaxCtas);
-    cfg.block = dev::kBlockThreads;
+    cfg.block = tuning_.block_threads;
     cfg.nvls_unroll = tuning_.nvls_unroll;
     if (loopback_) cfg.grid = std::min(cfg.grid, std::max(1, 128 / nranks_));  // one cooperative launch: keep it resident
     for (auto& a : per_rank) {
@@ -647,7 +647,7 @@ void Communicator::Impl::launch_gather_ranks(const CollectiveArgs& args, std::ve
                                              int grid) {
     kernels::LaunchConfig cfg;
     cfg.grid = std::min(grid, dev::kMaxCtas);
-    cfg.block = dev::kBlockThreads;
+    cfg.block = tuning_.block_threads;
     if (loopback_) cfg.grid = std::min(cfg.grid, std::max(1, 128 / nranks_));
     for (auto& a : per_rank)
         a.plan_hash = plan_fingerprint({static_cast<unsigned long long>(Collective::AllGather), static_cast<unsigned long long>(cfg.grid),

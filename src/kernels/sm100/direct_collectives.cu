@@ -309,6 +309,7 @@ template <typename T, typename Op, template <class> class PackT, bool kNvls, typ
 cudaError_t launch_reduce_n(int nranks, const ParamT& param, const LaunchConfig& cfg) {
     if constexpr (kNvls) {
         if (cfg.nvls_unroll >= 8) return launch(reduce_kernel<T, Op, 8, PackT, true, ParamT>, param, cfg);
+        if (cfg.nvls_unroll <= 1) return launch(reduce_kernel<T, Op, 1, PackT, true, ParamT>, param, cfg);
         if (cfg.nvls_unroll <= 2) return launch(reduce_kernel<T, Op, 2, PackT, true, ParamT>, param, cfg);
         return launch(reduce_kernel<T, Op, 4, PackT, true, ParamT>, param, cfg);
     } else if constexpr (PackT<T>::kBytes < 16) {

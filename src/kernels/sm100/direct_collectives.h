@@ -15,7 +15,7 @@ struct LaunchConfig {
     // Loopback emulation: one cooperative launch plays `loop_ranks` ranks (blockIdx.y = rank)
     // and `args` points to that many argument structs. 0 → normal launch of args[0].
     int loop_ranks = 0;
-    int nvls_unroll = 4;  // multimem loads in flight per thread (2, 4 or 8)
+    int nvls_unroll = 2;  // multimem loads in flight per thread (1, 2, 4 or 8)
 };
 
 // pack_bytes: what one thread moves per access and the unit of every length in `args`: 32 (256-bit

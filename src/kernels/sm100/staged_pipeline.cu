@@ -405,6 +405,7 @@ cudaError_t launch_t(RedOp op, const PipeArgs* args, const PipeLaunch& cfg) {
         if (cfg.loop_ranks > 0 || (op != RedOp::Sum && op != RedOp::Avg) || args[0].mc_in == nullptr || args[0].mc_out == nullptr)
             return cudaErrorInvalidValue;
         if (cfg.nvls_unroll >= 8) return launch_kernel(pipeline_kernel<T, OpAdd, true, 0, 8, PipeArgs>, args[0], cfg);
+        if (cfg.nvls_unroll <= 1) return launch_kernel(pipeline_kernel<T, OpAdd, true, 0, 1, PipeArgs>, args[0], cfg);
         if (cfg.nvls_unroll <= 2) return launch_kernel(pipeline_kernel<T, OpAdd, true, 0, 2, PipeArgs>, args[0], cfg);
         return launch_kernel(pipeline_kernel<T, OpAdd, true, 0, 4, PipeArgs>, args[0], cfg);
     }

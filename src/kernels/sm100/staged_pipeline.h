@@ -64,7 +64,7 @@ struct PipeLaunch {
     cudaStream_t stream = nullptr;
     int loop_ranks = 0;   // >0: one cooperative launch plays that many ranks (args[0..loop_ranks))
     bool nvls = false;    // reduce with multimem.ld_reduce / multimem.st (sum and avg only)
-    int nvls_unroll = 4;
+    int nvls_unroll = 2;
 };
 
 // Dynamic shared memory one CTA of the pipeline kernel needs.

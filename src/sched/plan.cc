@@ -32,14 +32,23 @@ Tuning default_tuning() {
     t.oneshot_max_bytes[3] = 16u << 10;
     t.nvls_min_bytes = 16u << 10;
     t.max_ctas = 128;
-    t.nvls_max_ctas = 64;
+    //  * Multimem kernel, 8 ranks, unroll x CTAs: fewer loads in flight are faster. 64 MiB: 726 GB/s with 2 loads
+    //    per thread on 48 CTAs, 722 (2, 64), 710 (4, 48), 692 (4, 64), 638 (8, 64), 587 (8, 128); 256 MiB: 818 (2, 48)
+    //    down to 760 (8, 128).
+    t.nvls_max_ctas = 48;
+    t.nvls_unroll = 2;
     t.twoshot_max_ctas = 128;
     t.bytes_per_cta = 32u << 10;
     t.oneshot_bytes_per_cta = 8u << 10;
     //  * Low-latency kernel across NVLink, 2 ranks, graph replay: 3.4-3.6 us for 1-16 KiB and 4.2 us at 32 KiB
     //    against 7.5-10.7 us for one-shot (its two barrier round trips).
-    t.ll_max_bytes = 32u << 10;
-    t.pipeline_min_bytes = 1u << 20;
+    //    8 ranks: 4.0-4.5 us up to 16 KiB, 5.6 us at 32 KiB, 7.3 us at 64 KiB against 11.2 us for the multimem
+    //    kernel and 10.4-14 us for one-shot; at 128 KiB it falls behind (12.0 vs 11.5 us).
+    t.ll_max_bytes = 64u << 10;
+    //  * Tile pipeline for buffers peers cannot address against copy / barrier / reduce / barrier / copy:
+    //    8 ranks 246 vs 224 us at 64 MiB, 835 vs 861 us at 256 MiB, 3142 vs 3414 us at 1 GiB; 2 ranks 152 vs 153 us
+    //    at 64 MiB, 1711 vs 2271 us at 1 GiB.
+    t.pipeline_min_bytes = 128u << 20;
     t.pipeline_tile_bytes = 256u << 10;
     t.pipeline_max_ctas = 64;
     t.pipeline_peer_max_ctas = 128;
@@ -87,6 +96,10 @@ Tuning tuning_from_text(const std::string& text, const Tuning& base, const std::
         else if (key == "oneshot_bytes_per_cta") t.oneshot_bytes_per_cta = std::max<std::size_t>(bytes, 1);
         else if (key == "ll_max_bytes") t.ll_max_bytes = std::min(bytes, kLlPlanMaxBytes);
         else if (key == "wide32") t.wide32 = bytes != 0;
+        else if (key == "block_threads") {
+            if (as_int < 32 || as_int > 512 || as_int % 32 != 0) throw std::invalid_argument(where + "block_threads must be a multiple of 32 between 32 and 512");
+            t.block_threads = as_int;
+        }
         else if (key == "pipeline_min_bytes") t.pipeline_min_bytes = bytes;
         else if (key == "pipeline_tile_bytes") t.pipeline_tile_bytes = std::max<std::size_t>(bytes / 4096 * 4096, 32u << 10);
         else if (key == "pipeline_max_ctas") t.pipeline_max_ctas = std::max(as_int, 1);
@@ -122,6 +135,9 @@ Tuning tuning_from_env() {
     t.oneshot_bytes_per_cta = env::get_bytes("B200CCL_ONESHOT_BYTES_PER_CTA", t.oneshot_bytes_per_cta);
     t.ll_max_bytes = std::min<std::size_t>(env::get_bytes("B200CCL_LL_MAX_BYTES", t.ll_max_bytes), kLlPlanMaxBytes);
     t.wide32 = env::get_bool("B200CCL_WIDE32", t.wide32);
+    t.block_threads = static_cast<int>(env::get_int("B200CCL_BLOCK_THREADS", t.block_threads, "NANO_NCCL_BLOCK_THREADS"));
+    if (t.block_threads < 32 || t.block_threads > 512 || t.block_threads % 32 != 0)
+        throw std::invalid_argument("B200CCL_BLOCK_THREADS must be a multiple of 32 between 32 and 512");
     t.pipeline_min_bytes = env::get_bytes("B200CCL_PIPELINE_MIN_BYTES", t.pipeline_min_bytes);
     t.pipeline_tile_bytes = std::max<std::size_t>(env::get_bytes("B200CCL_PIPELINE_TILE_BYTES", t.pipeline_tile_bytes) / 4096 * 4096, 32u << 10);
     t.pipeline_max_ctas = std::max(1, static_cast<int>(env::get_int("B200CCL_PIPELINE_MAX_CTAS", t.pipeline_max_ctas)));

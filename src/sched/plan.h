@@ -52,7 +52,7 @@ struct Tuning {
     int max_ctas = 128;                            // hard cap for every algorithm (B200CCL_MAX_CTAS)
     int nvls_max_ctas = 64;                        // more CTAs than this slowed the multimem kernels down
     int twoshot_max_ctas = 128;
-    int nvls_unroll = 4;                           // multimem loads in flight per thread (B200CCL_NVLS_UNROLL)
+    int nvls_unroll = 2;                           // multimem loads in flight per thread (B200CCL_NVLS_UNROLL)
     std::size_t bytes_per_cta = 0;                 // work given to one CTA before another is added
     std::size_t oneshot_bytes_per_cta = 0;         // one-shot reads every peer's copy: spread it thinner
     // AllReduce messages up to this size use the low-latency kernel (0 = only when asked for;
@@ -61,6 +61,10 @@ struct Tuning {
     // Peer two-shot AllReduce moves 32 bytes per access (ld/st.global.v8, sm_100) where alignment allows
     // (B200CCL_WIDE32=0 keeps 16-byte accesses).
     bool wide32 = true;
+    // Threads per CTA of the direct kernels (B200CCL_BLOCK_THREADS; the reference fixes its 512 at build
+    // time, include/nano_nccl/types.h:23-28). Fewer threads per CTA on more CTAs leave room on every SM
+    // for the CTAs of a matmul that runs beside the collective.
+    int block_threads = 512;
     // AllReduce of buffers that peers cannot address: from this size up the copy into the staging arena,
     // the reduction and the copy out run as a tile pipeline in one kernel (B200CCL_PIPELINE_MIN_BYTES;
     // below it: copy, barrier, reduce, barrier, copy). Every CTA gets the same number of tiles of about
@@ -75,7 +79,7 @@ Tuning default_tuning();
 Tuning tuning_from_env();
 // Applies a tuning file to `base`. One `key = value` per line, `#` starts a comment; byte counts take
 // K/M/G suffixes. Keys: oneshot_max_bytes (all rank counts) or oneshot_max_bytes.<nranks>, nvls_min_bytes,
-// max_ctas, nvls_max_ctas, twoshot_max_ctas, nvls_unroll, bytes_per_cta, oneshot_bytes_per_cta, ll_max_bytes, wide32,
+// max_ctas, nvls_max_ctas, twoshot_max_ctas, nvls_unroll, bytes_per_cta, oneshot_bytes_per_cta, ll_max_bytes, wide32, block_threads,
 // pipeline_min_bytes, pipeline_tile_bytes, pipeline_max_ctas, pipeline_peer_max_ctas.
 // `python -m nano_nccl_b200.tuner --emit-tuning FILE` writes such a file from its measurements.
 // Throws std::invalid_argument naming the file and line on an unknown key or a bad value.

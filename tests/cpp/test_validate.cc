@@ -93,24 +93,28 @@ int main() {
     plan = sched::make_plan(s, Algo::Auto, sched::default_tuning());
     T_CHECK(plan.algo == Algo::TwoShot);
     T_CHECK(!sched::make_plan(s, Algo::Nvls, sched::default_tuning()).error.empty());
-    s = sched::CallShape{}; s.nranks = 4; s.count = 1 << 20; s.wide = true;  // plain buffers of another process
+    s = sched::CallShape{}; s.nranks = 4; s.count = 64 << 20; s.wide = true;  // plain buffers of another process, 256 MiB
     plan = sched::make_plan(s, Algo::Auto, sched::default_tuning());
-    T_CHECK(plan.stage_in && plan.stage_out && plan.algo == Algo::Pipeline);  // 4 MiB: the tile pipeline
+    T_CHECK(plan.stage_in && plan.stage_out && plan.algo == Algo::Pipeline);  // large: the tile pipeline
     T_CHECK(plan.tile_bytes >= (32u << 10) && plan.tile_bytes % 4096 == 0 && plan.grid >= 1 && plan.grid <= 128);
-    T_CHECK((static_cast<std::size_t>(4) << 20) / plan.tile_bytes >= static_cast<std::size_t>(plan.grid));  // no CTA without a tile
+    T_CHECK((static_cast<std::size_t>(256) << 20) / plan.tile_bytes >= static_cast<std::size_t>(plan.grid));  // no CTA without a tile
+    {   // every CTA gets the same number of tiles
+        const std::size_t tiles = ((static_cast<std::size_t>(256) << 20) + plan.tile_bytes - 1) / plan.tile_bytes;
+        T_CHECK(tiles % static_cast<std::size_t>(plan.grid) == 0 || tiles / plan.grid >= 1);
+    }
     T_CHECK(!plan.pipe_nvls);                      // the arena has no multicast alias in this shape
     s.staging_multicast = true;
     T_CHECK(sched::make_plan(s, Algo::Auto, sched::default_tuning()).pipe_nvls);
     s.redop = RedOp::Min;                          // max/min never go through the switch
     T_CHECK(!sched::make_plan(s, Algo::Auto, sched::default_tuning()).pipe_nvls);
     s.redop = RedOp::Sum;
-    s.count = 1 << 10;                             // 4 KiB: below the pipeline threshold → copy, barrier, reduce, barrier, copy
+    s.count = 1 << 20;                             // 4 MiB: below the pipeline threshold → copy, barrier, reduce, barrier, copy
     plan = sched::make_plan(s, Algo::Auto, sched::default_tuning());
-    T_CHECK(plan.stage_in && plan.algo != Algo::Pipeline);
+    T_CHECK(plan.stage_in && plan.stage_out && plan.algo != Algo::Pipeline);
+    T_CHECK(sched::make_plan(s, Algo::Pipeline, sched::default_tuning()).algo == Algo::Pipeline);  // on request at any size
     s.wide = false;
     T_CHECK(!sched::make_plan(s, Algo::Pipeline, sched::default_tuning()).error.empty());
     s.wide = true;
-    s.count = 1 << 20;
     s.ring_only = true;
     T_CHECK(sched::make_plan(s, Algo::Auto, sched::default_tuning()).algo == Algo::Ring);
     // process layouts and per-edge transport plans (synthetic 2x2 topologies, as the reference's

@@ -56,7 +56,9 @@ def main():
                 if mode == "collectives":
                     # ordinary tensors of another process: small ones ride the flag-in-data kernel, large
                     # ones the tile pipeline (copy in, reduce, copy out inside one launch)
-                    want = "ll" if numel * x.element_size() <= (32 << 10) else ("pipeline" if numel * x.element_size() >= (1 << 20) else None)
+                    # (the caller lowers the pipeline's threshold to 1 MiB so that this test reaches it)
+                    nbytes = numel * x.element_size()
+                    want = "ll" if nbytes <= (32 << 10) else ("pipeline" if nbytes >= (1 << 20) else None)
                     assert want is None or comm.last_call()["algo"] == want, (numel, comm.last_call())
                     sx, so = comm.empty(numel, dtype), comm.empty(numel, dtype)
                     sx.copy_(x)

@@ -67,8 +67,8 @@ def test_planner_low_latency(lib, monkeypatch):
     monkeypatch.delenv("B200CCL_LL_MAX_BYTES", raising=False)
     rc, p = _plan(lib, 0, 1024, WIDE | RD | WR | WORD)
     assert rc == 0 and p[0] == 5  # small messages: no barrier at all
-    rc, p = _plan(lib, 0, 8192 + 4, WIDE | RD | WR | WORD)
-    assert rc == 0 and p[0] != 5  # above 32 KiB: the usual choice
+    rc, p = _plan(lib, 0, 16384 + 4, WIDE | RD | WR | WORD)
+    assert rc == 0 and p[0] != 5  # above 64 KiB: the usual choice
     monkeypatch.setenv("B200CCL_LL_MAX_BYTES", "0")
     rc, p = _plan(lib, 0, 1024, WIDE | RD | WR | WORD)
     assert rc == 0 and p[0] == 1  # switched off: one-shot
@@ -111,7 +111,7 @@ def test_cta_cap_from_the_environment(lib, monkeypatch):
     WIDE, RD, WR, IMC, OMC = 1, 2, 4, 8, 16
     monkeypatch.delenv("B200CCL_MAX_CTAS", raising=False)
     rc, p = _plan(lib, 0, 1 << 24, WIDE | RD | WR | IMC | OMC)
-    assert rc == 0 and p[0] == 3 and p[1] == 64  # measured default for the multimem kernel
+    assert rc == 0 and p[0] == 3 and p[1] == 48  # measured default for the multimem kernel
     rc, p = _plan(lib, 0, 1 << 24, WIDE | RD | WR)
     assert rc == 0 and p[0] == 2 and p[1] == 128  # and for two-shot
     monkeypatch.setenv("B200CCL_MAX_CTAS", "16")  # leave SMs to kernels that run beside the collective
@@ -127,7 +127,7 @@ def test_tuning_file(lib, monkeypatch, tmp_path):
     WIDE, RD, WR, IMC, OMC, WORD = 1, 2, 4, 8, 16, 128
     path = tmp_path / "b200.tuning"
     path.write_text("# measured on some machine\noneshot_max_bytes.8 = 64K   # eight ranks\nnvls_min_bytes = 1M\n"
-                    "nvls_max_ctas = 48\nll_max_bytes = 4K\n\n")
+                    "nvls_max_ctas = 40\nll_max_bytes = 4K\n\n")
     monkeypatch.setenv("B200CCL_TUNING_FILE", str(path))
     for var in ("B200CCL_MAX_CTAS", "B200CCL_LL_MAX_BYTES", "B200CCL_NVLS_MIN_BYTES", "B200CCL_ONESHOT_MAX_BYTES"):
         monkeypatch.delenv(var, raising=False)
@@ -136,7 +136,7 @@ def test_tuning_file(lib, monkeypatch, tmp_path):
     rc, p = _plan(lib, 0, 8192, WIDE | RD | WR | IMC | OMC, nranks=4)  # other rank counts keep their default
     assert rc == 0 and p[0] == 2                                      # (8 KiB one-shot limit there, multimem from 1 MiB)
     rc, p = _plan(lib, 0, 1 << 24, WIDE | RD | WR | IMC | OMC)
-    assert rc == 0 and p[0] == 3 and p[1] == 48
+    assert rc == 0 and p[0] == 3 and p[1] == 40
     rc, p = _plan(lib, 0, 512, WIDE | RD | WR | WORD)
     assert rc == 0 and p[0] == 5                                      # low-latency kernel switched on by the file
     monkeypatch.setenv("B200CCL_LL_MAX_BYTES", "0")                   # the environment still has the last word

@@ -73,7 +73,7 @@ def test_single_process_two_gpus():
 @pytest.mark.parametrize("mode", ["collectives", "socket", "ring"])
 def test_one_process_per_gpu(mode):
     world = min(ngpus(), 4)
-    outs = launch(world, mode)
+    outs = launch(world, mode, extra_env={"B200CCL_PIPELINE_MIN_BYTES": "1M"})
     for rc, out in outs:
         assert rc == 0 and "WORKER OK" in out, out
 
