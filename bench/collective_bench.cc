@@ -3,6 +3,7 @@
 // are --collective, --nranks, --loopback, --symmetric, --graph, --data and --json. Exit status is
 // non-zero when any row has #wrong != 0, as in the reference (all_reduce_bench.cu:414-419).
 #include "b200ccl/bench.h"
+#include "b200ccl/bootstrap.h"
 
 #include <cstdio>
 #include <cstdlib>
@@ -18,7 +19,9 @@ void usage(const char* argv0) {
                  "Usage: %s [--collective all_reduce|reduce_scatter|all_gather] [--algo auto|oneshot|twoshot|nvls|ring]\n"
                  "          [--dtype float|fp16|bf16] [--redop sum|avg|max|min] [--transport auto|shm|p2p|rdma]\n"
                  "          [--nranks N] [--loopback] [--symmetric] [--graph] [--data uniform|normal]\n"
-                 "          [-b bytes] [-e bytes] [-f factor] [-w warmup] [-n iters] [--json file]\n",
+                 "          [-b bytes] [-e bytes] [-f factor] [-w warmup] [-n iters] [--json file]\n"
+                 "          [--world W --rank R --addr HOST:PORT [--device D]]   one process per GPU: start W copies,\n"
+                 "          ranks 0..W-1, all naming rank 0's address; inputs are the constant rank+1 (--symmetric allowed)\n",
                  argv0);
 }
 
@@ -39,7 +42,8 @@ bool size_arg(const char* text, std::size_t* out) {
 
 int main(int argc, char** argv) {
     BenchConfig cfg;
-    std::string json_path;
+    std::string json_path, addr = "127.0.0.1:29400";
+    int world = 1, rank = 0, device = -1;
     for (int i = 1; i < argc; ++i) {
         const std::string a = argv[i];
         auto next = [&]() -> const char* { return i + 1 < argc ? argv[++i] : nullptr; };
@@ -60,6 +64,10 @@ int main(int argc, char** argv) {
         else if (a == "-w") { const char* v = next(); ok = v; if (v) cfg.warmup_iters = std::atoi(v); }
         else if (a == "-n") { const char* v = next(); ok = v; if (v) cfg.iters = std::atoi(v); }
         else if (a == "--json") { const char* v = next(); ok = v; if (v) json_path = v; }
+        else if (a == "--world") { const char* v = next(); ok = v; if (v) world = std::atoi(v); }
+        else if (a == "--rank") { const char* v = next(); ok = v; if (v) rank = std::atoi(v); }
+        else if (a == "--device") { const char* v = next(); ok = v; if (v) device = std::atoi(v); }
+        else if (a == "--addr") { const char* v = next(); ok = v; if (v) addr = v; }
         else ok = false;
         if (!ok) { usage(argv[0]); return 2; }
     }
@@ -68,12 +76,21 @@ int main(int argc, char** argv) {
 
     std::vector<BenchResult> results;
     int rc = 0;
+    const bool distributed = world > 1;
     try {
-        rc = run_collective_bench(cfg, &results);
+        if (distributed) {
+            const auto colon = addr.rfind(':');
+            if (colon == std::string::npos || rank < 0 || rank >= world) { usage(argv[0]); return 2; }
+            auto bootstrap = create_tcp_bootstrap(addr.substr(0, colon), std::atoi(addr.c_str() + colon + 1), rank, world);
+            rc = run_distributed_bench(*bootstrap, device >= 0 ? device : rank, cfg, &results);
+        } else {
+            rc = run_collective_bench(cfg, &results);
+        }
     } catch (const std::exception& e) {
         std::fprintf(stderr, "bench failed: %s\n", e.what());
         rc = 1;
     }
+    if (distributed && rank != 0) return rc;  // every process holds the same rows; rank 0 prints them
     std::printf("# b200ccl collective_bench\n");
     std::printf("# collective %s algo %s dtype %s redop %s transport %s nGpus %d warmup iters: %d iters: %d validation: 1 timing: device events, max over ranks\n",
                 collective_name(cfg.collective), cfg.algo.c_str(), dtype_name(cfg.dtype), redop_name(cfg.redop),

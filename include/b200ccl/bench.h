@@ -13,8 +13,15 @@
 
 namespace b200ccl {
 
+class Bootstrap;
+
 // Returns 0 on success (results appended), non-zero when the run could not be made.
 int run_collective_bench(const BenchConfig& config, std::vector<BenchResult>* results);
+// One process per GPU, joined by `bootstrap`: constant inputs of value global_rank + 1, a barrier
+// before the timed batch, the slowest rank's device time, every rank's wrong elements, and one
+// return value agreed between all processes (the MPI variant of the reference's benchmark,
+// benchmarks/all_reduce_bench.cu:84-316). Every process appends the same rows to `results`.
+int run_distributed_bench(Bootstrap& bootstrap, int device, const BenchConfig& config, std::vector<BenchResult>* results);
 // Same name as the reference's entry point; AllReduce only.
 int run_all_reduce_bench(const BenchConfig& config, std::vector<BenchResult>* results);
 

@@ -54,3 +54,25 @@ def test_rdma_ab_parsing_summary_and_dry_run(tmp_path, capsys):
     assert rc == 0 and len(out) == 2
     assert "B200CCL_RDMA_USE_WRITE=1" in out[0] and "B200CCL_RDMA_SHARED_PROGRESS=1" in out[0] and "--transport rdma" in out[0]
     assert "B200CCL_RDMA_GDR=1" in out[1] and "--nranks 4 --loopback" in out[1]
+
+
+def test_native_multi_process_benchmark_agrees_on_a_setup_failure():
+    # Two processes of the command-line benchmark on a machine without a GPU: the communicator cannot
+    # be created, every process learns of it through the rendezvous and all leave with the same status
+    # instead of one waiting for the other.
+    import socket
+    import subprocess
+    import pytest
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    binary = os.path.join(root, "build", "bin", "b200ccl_collective_bench")
+    if not os.path.exists(binary):
+        pytest.skip("native benchmark not built")
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    procs = [subprocess.Popen([binary, "--world", "2", "--rank", str(r), "--addr", f"127.0.0.1:{port}", "-b", "1024", "-e", "1024"],
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [(p.wait(timeout=120), p.stdout.read()) for p in procs]
+    assert [rc for rc, _ in outs] == [3, 3], outs
+    assert all("communicator setup failed" in out for _, out in outs), outs

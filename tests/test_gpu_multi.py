@@ -224,3 +224,34 @@ def test_pairs_without_peer_access_fall_back_edge_by_edge(monkeypatch):
         comm.close()
     with pytest.raises(Exception, match="cannot access"):
         nn.Communicator(devices=devices, transport="p2p")  # an explicit request fails rather than falling back
+
+
+@pytest.mark.skipif(ngpus() < 2, reason="needs two GPUs")
+def test_native_benchmark_one_process_per_gpu():
+    # The command-line benchmark in its multi-process form (the reference's MPI variant,
+    # benchmarks/all_reduce_bench.cu:84-316): constant inputs rank + 1, one table from rank 0,
+    # #wrong = 0 and the same exit status in every process.
+    binary = os.path.join(ROOT, "build", "bin", "b200ccl_collective_bench")
+    if not os.path.exists(binary):
+        pytest.skip("native benchmark not built")
+    world = min(ngpus(), 4)
+    for extra in (["--redop", "avg", "--dtype", "bf16"], ["--collective", "all_gather", "--symmetric"],
+                  ["--collective", "reduce_scatter", "--redop", "max"]):
+        port = free_port()
+        procs = [subprocess.Popen([binary, "--world", str(world), "--rank", str(r), "--addr", f"127.0.0.1:{port}", "-b", "4096",
+                                   "-e", "4194304", "-f", "32", "-w", "2", "-n", "5"] + extra,
+                                  env=dict(os.environ, B200CCL_WAIT_TIMEOUT_MS="5000"), stdout=subprocess.PIPE,
+                                  stderr=subprocess.STDOUT, text=True) for r in range(world)]
+        outs = []
+        for p in procs:
+            try:
+                out, _ = p.communicate(timeout=240)
+            except subprocess.TimeoutExpired:
+                p.kill()
+                out, _ = p.communicate()
+                out += "\n[killed after timeout]"
+            outs.append((p.returncode, out))
+        assert all(rc == 0 for rc, _ in outs), outs
+        rows = [line.split() for line in outs[0][1].splitlines() if line and not line.startswith("#")]
+        assert len(rows) == 3 and all(r[9] == "0" for r in rows), outs[0][1]   # three sizes, #wrong = 0
+        assert all(not [l for l in out.splitlines() if l and not l.startswith("#")] for _, out in outs[1:]), "only rank 0 prints rows"
