@@ -97,6 +97,13 @@ __device__ bool run_slice(const RingArgs& a, ChannelState& st, Shared& sm, unsig
     const T* fifo_in = recv ? static_cast<const T*>(st.ch.recv_fifo) + ring::slot_offset(st.recv_step, a.step_elems) : nullptr;
     T* fifo_out = send ? static_cast<T*>(st.ch.send_fifo) + ring::slot_offset(st.send_step, a.step_elems) : nullptr;
     u64 t_wait_recv = 0, t_wait_send = 0, t0 = 0;
+    // Small received slices (one 16-byte vector per thread at most) return their FIFO slot to the
+    // sender BEFORE they are combined and forwarded: the slot is read into registers, the credit is
+    // posted, and only then does the slice go on. On host-memory and network edges, where a credit
+    // takes microseconds to arrive, this takes the consumer's own work off the sender's critical path.
+    // Parity: the reference's early-credit path for slices of at most 4096 bytes
+    // (src/kernels/ring_simple_kernel.cuh:486-583, 912-927).
+    bool early = false;
 
     bool ok = true;
     if constexpr (kWide) {
@@ -118,10 +125,21 @@ __device__ bool run_slice(const RingArgs& a, ChannelState& st, Shared& sm, unsig
             return false;
         }
         if (st.ch.stats && threadIdx.x == 0) t0 = global_timer_ns();
+        early = recv && nvec <= (u64)kRingThreads;
+        uint4 pre = make_uint4(0, 0, 0, 0);
+        if (early) {
+            int sink = 0;
+            if (threadIdx.x < nvec) {
+                pre = ld16_volatile(reinterpret_cast<const uint4*>(fifo_in) + threadIdx.x);
+                sink = (pre.x ^ pre.y ^ pre.z ^ pre.w) == 0x5bd1e995u;  // a use of the value: the barrier below then follows the load's arrival
+            }
+            (void)__syncthreads_or(sink);  // every thread holds its part of the slot
+            if (threadIdx.x == 0) st_release_sys(st.ch.recv_head, st.recv_step + ring::kSliceSteps);
+        }
         auto combine_store = [&](u64 v, uint4 loc, bool have_loc) {
             uint4 out;
             if (recv) {
-                const uint4 r = ld16_volatile(reinterpret_cast<const uint4*>(fifo_in) + v);
+                const uint4 r = early ? pre : ld16_volatile(reinterpret_cast<const uint4*>(fifo_in) + v);
                 if (have_loc || scaled) {
                     float acc[kElems], f[kElems];
                     Wide<T>::unpack(r, acc);
@@ -194,7 +212,7 @@ __device__ bool run_slice(const RingArgs& a, ChannelState& st, Shared& sm, unsig
     u64 t1 = 0;
     if (st.ch.stats && threadIdx.x == 0) t1 = global_timer_ns();
     if (recv) {
-        if (threadIdx.x == 0) st_release_sys(st.ch.recv_head, st.recv_step + ring::kSliceSteps);
+        if (!early && threadIdx.x == 0) st_release_sys(st.ch.recv_head, st.recv_step + ring::kSliceSteps);
         st.recv_step += ring::kSliceSteps;
     }
     if (send) {

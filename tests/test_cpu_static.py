@@ -66,6 +66,9 @@ def test_step_counters_use_system_scope_release_acquire():
     # data stores of the whole CTA are ordered before the counter by a block barrier, then release
     publish = ring[ring.index("// Publish:"):]
     assert publish.index("__syncthreads()") < publish.index("st_release_sys(st.ch.recv_head") < publish.index("st_release_sys(st.ch.send_tail")
+    # the early credit of small slices is posted only after every thread holds its part of the slot
+    early = ring[ring.index("if (early) {"):ring.index("auto combine_store")]
+    assert early.index("ld16_volatile(") < early.index("__syncthreads_or(") < early.index("st_release_sys(st.ch.recv_head")
 
 
 def test_low_latency_kernel_waits_are_bounded_and_flags_travel_with_the_data():

@@ -168,3 +168,39 @@ def test_staged_pipeline_all_reduce(ranks, dtype):
                 assert torch.equal(o, outs[0])
     finally:
         comm.close()
+
+
+@pytest.mark.parametrize("ranks", [2, 4, 8])
+@pytest.mark.parametrize("transport", ["auto", "shm"])
+def test_ring_small_slices_return_their_credit_early(ranks, transport):
+    # Messages whose slices hold at most one 16-byte vector per thread take the early-credit path
+    # of the ring kernel (slot read into registers, credit posted, then combined and forwarded).
+    # Many calls in a row reuse every FIFO slot several times, so a credit posted too early would
+    # let the sender overwrite a slot that is still being read and corrupt a later call.
+    comm = nn.Communicator(devices=[0], loopback_ranks=ranks, algo="ring", transport=transport, channels=4, wait_timeout_ms=3000)
+    try:
+        for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 1e-1)):
+            for i, numel in enumerate([1024, 4096, 16384, 2048, 65536, 4096, 1024, 8192] * 3):
+                op = ["sum", "avg", "max", "min"][i % 4]
+                gen = torch.Generator(device="cuda").manual_seed(300 + i)
+                ins = [torch.randn(numel, device="cuda", generator=gen).to(dtype) for _ in range(ranks)]
+                outs = [torch.full_like(t, float("nan")) for t in ins]
+                comm.all_reduce(outs, ins, op=op)
+                stack = torch.stack([t.float() for t in ins])
+                ref = {"sum": stack.sum(0), "avg": stack.sum(0) / ranks, "max": stack.max(0).values, "min": stack.min(0).values}[op]
+                for o in outs:
+                    assert (o.float() - ref).abs().max().item() <= tol * (2 if dtype != torch.float32 else 1), (numel, op)
+        blk = 2048
+        ins = [torch.randn(blk * ranks, device="cuda") for _ in range(ranks)]
+        rs = [torch.empty(blk, device="cuda") for _ in range(ranks)]
+        ag = [torch.empty(blk * ranks * ranks, device="cuda") for _ in range(ranks)]
+        comm.reduce_scatter(rs, ins)
+        comm.all_gather(ag, ins)
+        torch.cuda.synchronize()
+        comm.check_async_error()
+        total = torch.stack(ins).sum(0)
+        for r in range(ranks):
+            assert (rs[r] - total[r * blk:(r + 1) * blk]).abs().max().item() <= 1e-5
+            assert torch.equal(ag[r], torch.cat(ins))
+    finally:
+        comm.close()
