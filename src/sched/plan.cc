@@ -44,7 +44,10 @@ Tuning default_tuning() {
     //    against 7.5-10.7 us for one-shot (its two barrier round trips).
     //    8 ranks: 4.0-4.5 us up to 16 KiB, 5.6 us at 32 KiB, 7.3 us at 64 KiB against 11.2 us for the multimem
     //    kernel and 10.4-14 us for one-shot; at 128 KiB it falls behind (12.0 vs 11.5 us).
+    //    4 ranks: 3.7-4.0 us up to 16 KiB, 6.6 us at 64 KiB (multimem 11.6), 9.7 us at 128 KiB (14.0);
+    //    2 ranks: 3.3-3.5 us up to 16 KiB, 8.3 us at 128 KiB (two-shot 12.0).
     t.ll_max_bytes = 64u << 10;
+    t.ll_max_bytes_upto4 = 128u << 10;
     //  * Tile pipeline for buffers peers cannot address against copy / barrier / reduce / barrier / copy:
     //    8 ranks 246 vs 224 us at 64 MiB, 835 vs 861 us at 256 MiB, 3142 vs 3414 us at 1 GiB; 2 ranks 152 vs 153 us
     //    at 64 MiB, 1711 vs 2271 us at 1 GiB.
@@ -94,7 +97,8 @@ Tuning tuning_from_text(const std::string& text, const Tuning& base, const std::
         else if (key == "nvls_unroll") t.nvls_unroll = as_int;
         else if (key == "bytes_per_cta") t.bytes_per_cta = std::max<std::size_t>(bytes, 1);
         else if (key == "oneshot_bytes_per_cta") t.oneshot_bytes_per_cta = std::max<std::size_t>(bytes, 1);
-        else if (key == "ll_max_bytes") t.ll_max_bytes = std::min(bytes, kLlPlanMaxBytes);
+        else if (key == "ll_max_bytes") t.ll_max_bytes = t.ll_max_bytes_upto4 = std::min(bytes, kLlPlanMaxBytes);
+        else if (key == "ll_max_bytes_upto4") t.ll_max_bytes_upto4 = std::min(bytes, kLlPlanMaxBytes);
         else if (key == "wide32") t.wide32 = bytes != 0;
         else if (key == "block_threads") {
             if (as_int < 32 || as_int > 512 || as_int % 32 != 0) throw std::invalid_argument(where + "block_threads must be a multiple of 32 between 32 and 512");
@@ -133,7 +137,8 @@ Tuning tuning_from_env() {
     t.nvls_unroll = static_cast<int>(env::get_int("B200CCL_NVLS_UNROLL", t.nvls_unroll));
     t.bytes_per_cta = env::get_bytes("B200CCL_BYTES_PER_CTA", t.bytes_per_cta);
     t.oneshot_bytes_per_cta = env::get_bytes("B200CCL_ONESHOT_BYTES_PER_CTA", t.oneshot_bytes_per_cta);
-    t.ll_max_bytes = std::min<std::size_t>(env::get_bytes("B200CCL_LL_MAX_BYTES", t.ll_max_bytes), kLlPlanMaxBytes);
+    if (env::get("B200CCL_LL_MAX_BYTES"))
+        t.ll_max_bytes = t.ll_max_bytes_upto4 = std::min<std::size_t>(env::get_bytes("B200CCL_LL_MAX_BYTES", 0), kLlPlanMaxBytes);
     t.wide32 = env::get_bool("B200CCL_WIDE32", t.wide32);
     t.block_threads = static_cast<int>(env::get_int("B200CCL_BLOCK_THREADS", t.block_threads, "NANO_NCCL_BLOCK_THREADS"));
     if (t.block_threads < 32 || t.block_threads > 512 || t.block_threads % 32 != 0)
@@ -236,7 +241,7 @@ Plan make_plan(const CallShape& s, Algo forced, const Tuning& t) {
         p.error = "algo ll takes 4-byte aligned all_reduce messages of at most 128 KiB";
         return p;
     }
-    if (forced == Algo::LowLatency || (forced == Algo::Auto && ll_fits && bytes <= t.ll_max_bytes)) {
+    if (forced == Algo::LowLatency || (forced == Algo::Auto && ll_fits && bytes <= (s.nranks <= 4 ? t.ll_max_bytes_upto4 : t.ll_max_bytes))) {
         p.algo = Algo::LowLatency;  // neither buffer needs to be peer-addressable: no staging
         p.grid = 8;
         return p;

@@ -58,6 +58,9 @@ struct Tuning {
     // AllReduce messages up to this size use the low-latency kernel (0 = only when asked for;
     // B200CCL_LL_MAX_BYTES; never above 128 KiB).
     std::size_t ll_max_bytes = 0;
+    // Up to four ranks the flag-in-data kernel carries less traffic per rank and stays ahead longer
+    // (B200CCL_LL_MAX_BYTES sets both limits).
+    std::size_t ll_max_bytes_upto4 = 0;
     // Peer two-shot AllReduce moves 32 bytes per access (ld/st.global.v8, sm_100) where alignment allows
     // (B200CCL_WIDE32=0 keeps 16-byte accesses).
     bool wide32 = true;
@@ -79,7 +82,8 @@ Tuning default_tuning();
 Tuning tuning_from_env();
 // Applies a tuning file to `base`. One `key = value` per line, `#` starts a comment; byte counts take
 // K/M/G suffixes. Keys: oneshot_max_bytes (all rank counts) or oneshot_max_bytes.<nranks>, nvls_min_bytes,
-// max_ctas, nvls_max_ctas, twoshot_max_ctas, nvls_unroll, bytes_per_cta, oneshot_bytes_per_cta, ll_max_bytes, wide32, block_threads,
+// max_ctas, nvls_max_ctas, twoshot_max_ctas, nvls_unroll, bytes_per_cta, oneshot_bytes_per_cta, ll_max_bytes, ll_max_bytes_upto4,
+// wide32, block_threads,
 // pipeline_min_bytes, pipeline_tile_bytes, pipeline_max_ctas, pipeline_peer_max_ctas.
 // `python -m nano_nccl_b200.tuner --emit-tuning FILE` writes such a file from its measurements.
 // Throws std::invalid_argument naming the file and line on an unknown key or a bad value.
