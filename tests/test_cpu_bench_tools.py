@@ -76,3 +76,21 @@ def test_native_multi_process_benchmark_agrees_on_a_setup_failure():
     outs = [(p.wait(timeout=120), p.stdout.read()) for p in procs]
     assert [rc for rc, _ in outs] == [3, 3], outs
     assert all("communicator setup failed" in out for _, out in outs), outs
+
+
+def test_bench_py_traffic_model_and_median():
+    # bench.py's per-direction NVLink byte model (link_fraction_of_900) and its batch statistics
+    spec = importlib.util.spec_from_file_location("bench_main", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    S = 64 << 20
+    assert bench.link_bytes_per_direction("nvls", S, 8) == S * 1.125       # own shard out once + the result back, self included
+    assert bench.link_bytes_per_direction("twoshot", S, 8) == S * 1.75     # pull 7/8, push 7/8
+    assert bench.link_bytes_per_direction("twoshot", S, 2) == S
+    assert bench.link_bytes_per_direction("oneshot", S, 4) == 3 * S
+    assert bench.link_bytes_per_direction("ll", 1024, 8) == 2 * 1024 * 7   # 8 bytes on the wire per 4 of data
+    assert bench.link_bytes_per_direction("copy", S, 1) == 0
+    assert bench.busbw(S, 1e-3, 8) == S / 1e-3 / 1e9 * 1.75 and bench.busbw(S, 1e-3, 1) == S / 1e-3 / 1e9
+    assert bench.median([3.0, 1.0, 2.0]) == 2.0 and bench.median([4.0, 1.0, 2.0, 3.0]) == 2.5
+    peak, kind = bench.measured_peaks()
+    assert peak > 1000 and kind in ("measured", "fallback")
