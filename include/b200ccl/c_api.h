@@ -109,6 +109,9 @@ int b2_selftest_wait(int kind, int device, double timeout_ms, int out[4], double
 /* A kernel writes a payload then releases a counter in mapped host memory; the host acquires the
  * counter and must see the payload. *ok = 1 when every round held. */
 int b2_selftest_publication(int device, int rounds, int* ok);
+/* A kernel publishes `slices` ring slices (payload, byte count, tail) into a mapped host FIFO with no
+ * proxy thread; the host consumes them and returns credits. *ok = 1 when every slot was consistent. */
+int b2_selftest_direct_send(int device, int slices, int* ok);
 
 #ifdef __cplusplus
 }

@@ -294,6 +294,10 @@ int b2_selftest_wait(int kind, int device, double timeout_ms, int out[4], double
     });
 }
 
+int b2_selftest_direct_send(int device, int slices, int* ok) {
+    return guarded([&] { *ok = kernels::selftest_direct_send(device, slices) ? 1 : 0; });
+}
+
 int b2_selftest_publication(int device, int rounds, int* ok) {
     return guarded([&] { *ok = kernels::selftest_publication(device, rounds) ? 1 : 0; });
 }

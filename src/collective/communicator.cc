@@ -100,6 +100,14 @@ private:
 
     void resolve_transport();
     void ensure_staging(const CollectiveArgs& args);
+    void allocate_staging();
+    // The two halves of rank p's staging arena (checking builds put a page of canary bytes before
+    // the first and after the second) and their multicast aliases.
+    char* stage_in_ptr(int p) const { return static_cast<char*>(stage_->rank_ptr(p)) + stage_guard_; }
+    char* stage_out_ptr(int p) const { return stage_in_ptr(p) + staging_half_; }
+    char* stage_mc_in() const { return static_cast<char*>(stage_->multicast_ptr()) + stage_guard_; }
+    char* stage_mc_out() const { return stage_mc_in() + staging_half_; }
+    void check_canaries() const;
     Located locate(const void* p, std::size_t bytes, int grank) const;
     void wait_previous(Local& l, cudaStream_t stream);
     void record_done(Local& l, cudaStream_t stream);
@@ -136,6 +144,7 @@ private:
     Algo forced_algo_ = Algo::Auto;
     unsigned long long timeout_ns_ = 0;
     std::size_t staging_half_ = 0;
+    std::size_t stage_guard_ = 0;  // bytes of canary before and after the arena (checking builds), else 0
     int channels_ = kDefaultChannels;
     sched::Tuning tuning_;
     sched::ProcessLayout layout_;
@@ -270,8 +279,7 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
         // cannot be addressed), and which call does is a per-rank fact: allocating it on first use
         // would leave a rank that needs it waiting, inside a collective allocation, for ranks that do not.
         if (multiprocess_ && nranks_ >= 2) {
-            stage_ = alloc_->allocate(staging_half_ * 2, "staging");
-            pipe_flags_ = alloc_->allocate(sizeof(dev::PipeFlags), "pipeline flags");
+            allocate_staging();
         }
     }
 
@@ -464,6 +472,7 @@ Communicator::Impl::~Impl() {
 }
 
 void Communicator::Impl::check_async_error() const {
+    if (latched_.empty()) check_canaries();
     if (latched_.empty() && ring_) {
         // The root cause first: a failed proxy raises the abort word, and the kernels that leave
         // their waits because of it only record the echo ("aborted").
@@ -507,8 +516,58 @@ void Communicator::Impl::ensure_staging(const CollectiveArgs& args) {
             throw std::runtime_error("the staging arena must be allocated outside a stream capture: run one collective on "
                                      "buffers of this kind before capturing, or use symmetric or registered buffers");
     }
-    stage_ = alloc_->allocate(staging_half_ * 2, "staging");
+    allocate_staging();
+}
+
+namespace {
+constexpr unsigned char kCanaryByte = 0xA5;
+}
+
+void Communicator::Impl::allocate_staging() {
+#if defined(B200CCL_DEBUG_BOUNDS)
+    stage_guard_ = 4096;
+#endif
+    stage_ = alloc_->allocate(staging_half_ * 2 + 2 * stage_guard_, "staging");
     pipe_flags_ = alloc_->allocate(sizeof(dev::PipeFlags), "pipeline flags");
+    if (stage_guard_ != 0) {
+        for (const auto& l : local_) {
+            DeviceGuard guard(l.device);
+            char* base = static_cast<char*>(stage_->rank_ptr(l.grank));
+            B2_CUDA(cudaMemset(base, kCanaryByte, stage_guard_));
+            B2_CUDA(cudaMemset(base + stage_guard_ + 2 * staging_half_, kCanaryByte, stage_guard_));
+        }
+        for (const auto& l : local_) {
+            DeviceGuard guard(l.device);
+            B2_CUDA(cudaDeviceSynchronize());
+        }
+        if (bootstrap_) bootstrap_->barrier();
+    }
+}
+
+// Checking builds: the canary pages around the arena must still hold their pattern. A kernel that
+// indexed past a half of the arena (on this rank or, through peer stores, from another) shows here.
+void Communicator::Impl::check_canaries() const {
+    if (stage_guard_ == 0 || !stage_) return;
+    std::vector<unsigned char> host(stage_guard_);
+    for (const auto& l : local_) {
+        DeviceGuard guard(l.device);
+        char* base = static_cast<char*>(stage_->rank_ptr(l.grank));
+#if defined(B200CCL_DEBUG_BOUNDS)
+        // Test hook: overwrite one canary byte from the host, as a stray store would.
+        if (env::get_bool("B200CCL_DEBUG_SMASH_CANARY", false)) B2_CUDA(cudaMemset(base + stage_guard_ + 2 * staging_half_ + 17, 0, 1));
+#endif
+        for (int side = 0; side < 2; ++side) {
+            const char* from = side == 0 ? base : base + stage_guard_ + 2 * staging_half_;
+            B2_CUDA(cudaMemcpy(host.data(), from, stage_guard_, cudaMemcpyDeviceToHost));
+            for (std::size_t i = 0; i < stage_guard_; ++i) {
+                if (host[i] != kCanaryByte) {
+                    poison("staging arena canary overwritten: rank " + std::to_string(l.grank) + ", byte " + std::to_string(i) +
+                           (side == 0 ? " of the page before the arena" : " of the page after the arena"));
+                    return;
+                }
+            }
+        }
+    }
 }
 
 Located Communicator::Impl::locate(const void* p, std::size_t bytes, int grank) const {
@@ -901,14 +960,14 @@ void Communicator::Impl::launch_pipeline(const CollectiveArgs& args, const sched
         a.user_in = args.send_buffers[i];
         a.user_out = args.recv_buffers[i];
         for (int p = 0; p < nranks_; ++p) {
-            a.arena_in[p] = stage_->rank_ptr(p);
-            a.arena_out[p] = static_cast<char*>(stage_->rank_ptr(p)) + staging_half_;
+            a.arena_in[p] = stage_in_ptr(p);
+            a.arena_out[p] = stage_out_ptr(p);
             a.ctrl[p] = static_cast<dev::ControlBlock*>(ctrl_->rank_ptr(p));
             a.flags[p] = static_cast<dev::PipeFlags*>(pipe_flags_->rank_ptr(p));
         }
         if (cfg.nvls) {
-            a.mc_in = stage_->multicast_ptr();
-            a.mc_out = static_cast<char*>(stage_->multicast_ptr()) + staging_half_;
+            a.mc_in = stage_mc_in();
+            a.mc_out = stage_mc_out();
         }
         a.status = local_[i].status;
         a.stats = pipe_stats_.empty() ? nullptr : pipe_stats_[i];
@@ -987,12 +1046,12 @@ void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sch
             if (args.redop == RedOp::Avg) a.scale = 1.0f / static_cast<float>(nranks_);
             for (int p = 0; p < nranks_; ++p) {
                 // input table
-                if (plan.stage_in) a.in[p] = stage_->rank_ptr(p);
+                if (plan.stage_in) a.in[p] = stage_in_ptr(p);
                 else if (in_win != nullptr)
                     a.in[p] = static_cast<const char*>(windows_[(*in_win)[i].region].ptr[p]) + (*in_win)[i].offset + off;
                 else if (direct) a.in[p] = static_cast<const char*>(args.send_buffers[p]) + off;
                 // output table
-                if (plan.stage_out) a.out[p] = static_cast<char*>(stage_->rank_ptr(p)) + staging_half_;
+                if (plan.stage_out) a.out[p] = stage_out_ptr(p);
                 else if (oneshot) a.out[p] = nullptr;
                 else if (out_win != nullptr)
                     a.out[p] = static_cast<char*>(windows_[(*out_win)[i].region].ptr[p]) + (*out_win)[i].offset + off;
@@ -1008,9 +1067,9 @@ void Communicator::Impl::launch_all_reduce(const CollectiveArgs& args, const sch
             a.in_extent -= std::min<std::size_t>(len, env::get_bytes("B200CCL_DEBUG_SHRINK_EXTENT", 0));
 #endif
             if (nvls) {
-                a.mc_in = plan.stage_in ? static_cast<const char*>(stage_->multicast_ptr())
+                a.mc_in = plan.stage_in ? static_cast<const char*>(stage_mc_in())
                                         : static_cast<const char*>(windows_[(*in_win)[i].region].mc) + (*in_win)[i].offset + off;
-                a.mc_out = plan.stage_out ? static_cast<char*>(stage_->multicast_ptr()) + staging_half_
+                a.mc_out = plan.stage_out ? stage_mc_out()
                                           : static_cast<char*>(windows_[(*out_win)[i].region].mc) + (*out_win)[i].offset + off;
             }
         }
@@ -1042,7 +1101,7 @@ void Communicator::Impl::launch_reduce_scatter(const CollectiveArgs& args, const
             a.uin_stride = block_packs;
             if (args.redop == RedOp::Avg) a.scale = 1.0f / static_cast<float>(nranks_);
             for (int p = 0; p < nranks_; ++p) {
-                if (plan.stage_in) a.in[p] = stage_->rank_ptr(p);
+                if (plan.stage_in) a.in[p] = stage_in_ptr(p);
                 else if (in_win != nullptr)
                     a.in[p] = static_cast<const char*>(windows_[(*in_win)[i].region].ptr[p]) + (*in_win)[i].offset + off;
                 else if (direct) a.in[p] = static_cast<const char*>(args.send_buffers[p]) + off;
@@ -1090,7 +1149,7 @@ void Communicator::Impl::launch_all_gather(const CollectiveArgs& args, const sch
             a.out_stride = block_packs;
             for (int p = 0; p < nranks_; ++p) {
                 if (plan.gather_mode == 1) {  // pull: need everyone's input
-                    if (plan.stage_in) a.in[p] = stage_->rank_ptr(p);
+                    if (plan.stage_in) a.in[p] = stage_in_ptr(p);
                     else if (in_win != nullptr)
                         a.in[p] = static_cast<const char*>(windows_[(*in_win)[i].region].ptr[p]) + (*in_win)[i].offset + off;
                     else if (direct) a.in[p] = static_cast<const char*>(args.send_buffers[p]) + off;

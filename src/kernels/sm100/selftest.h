@@ -14,5 +14,8 @@ struct SelfTestResult {
 SelfTestResult selftest_wait_timeout(int device, double timeout_ms);
 SelfTestResult selftest_abort(int device, double timeout_ms);
 bool selftest_publication(int device, int rounds);
+// Device-side "send" of `slices` slices into a mapped host FIFO with no proxy thread: the host plays
+// the proxy and checks tail, byte count and payload of every slot, returning credits as it goes.
+bool selftest_direct_send(int device, int slices);
 
 }  // namespace b200ccl::kernels

@@ -123,14 +123,4 @@ __device__ __forceinline__ bool cta_barrier_all_ranks(ControlBlock* const* ctrl,
     return __syncthreads_and(ok) != 0;
 }
 
-// The two halves of a barrier, for pipelines that signal early and wait late. `word` selects one
-// of a CTA's monotonic counters in every rank's flag block: row[src] of rank dst is written by src.
-__device__ __forceinline__ void signal_all_ranks(unsigned long long* const* rows, int rank, int nranks,
-                                                 unsigned long long value) {
-    // Caller: one thread per destination rank (lane p < nranks), after a barrier that orders the
-    // CTA's (or warp group's) stores before this release.
-    const int p = threadIdx.x & 31;
-    if (p < nranks) st_release_sys(rows[p] + rank, value);
-}
-
 }  // namespace b200ccl::dev

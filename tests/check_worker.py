@@ -3,7 +3,9 @@ caller before this process starts). Every failure here is made on the host; no G
 socket-fault — a send proxy closes its socket after two slices: the ring kernels must leave their
                waits, the error must name the edge, and the communicator must refuse new work;
 bounds       — the host is told to pass extents that are too short: the kernel must record the
-               first bad index, skip those accesses and still run to its end."""
+               first bad index, skip those accesses and still run to its end;
+canary       — the staging arena sits between two pages of canary bytes: they survive staged
+               collectives, and a byte overwritten from the host is reported."""
 import os
 import sys
 
@@ -59,6 +61,26 @@ def main():
         for o in outs:
             assert (o[:good] - ref[:good]).abs().max().item() <= 1e-5
             assert (o[good:] == -7.0).all()
+        comm.close()
+    elif mode == "canary":
+        smash = os.environ.pop("B200CCL_DEBUG_SMASH_CANARY", None)
+        comm = nn.Communicator(devices=[0], loopback_ranks=4, algo="pipeline", wait_timeout_ms=3000, staging_bytes=8 << 20)
+        for numel in (1 << 20, (3 << 20) + 4, 4096):
+            ins = [torch.randn(numel, device="cuda") for _ in range(4)]
+            outs = [torch.empty_like(t) for t in ins]
+            comm.all_reduce(outs, ins)
+            torch.cuda.synchronize()
+            comm.check_async_error()   # includes the canary check in this build
+            ref = torch.stack(ins).sum(0)
+            assert all((o - ref).abs().max().item() <= 1e-5 for o in outs)
+        if smash:
+            os.environ["B200CCL_DEBUG_SMASH_CANARY"] = "1"
+            try:
+                comm.check_async_error()
+                raise SystemExit("expected the canary check to fire")
+            except nn.B200CclError as e:
+                assert "canary overwritten" in str(e) and "after the arena" in str(e), str(e)
+                print("detected:", e)
         comm.close()
     print("WORKER OK")
 

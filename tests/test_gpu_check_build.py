@@ -32,6 +32,13 @@ def test_device_index_checks_record_and_skip():
     assert rc == 0 and "WORKER OK" in out, out
 
 
+def test_canary_pages_around_the_staging_arena():
+    rc, out = run("canary")
+    assert rc == 0 and "WORKER OK" in out, out
+    rc, out = run("canary", B200CCL_DEBUG_SMASH_CANARY="1")
+    assert rc == 0 and "WORKER OK" in out and "canary overwritten" in out, out
+
+
 def test_product_library_has_no_fault_hook():
     # In the product build the environment variable is ignored.
     code = ("import torch, nano_nccl_b200 as nn\n"

@@ -290,3 +290,14 @@ def test_release_acquire_publication():
     ok = ctypes.c_int()
     _lib.check(lib.b2_selftest_publication(0, 50, ctypes.byref(ok)))
     assert ok.value == 1
+
+
+def test_device_send_without_a_proxy():
+    # The sending side of a network edge, as a kernel on its own: payload into a mapped host FIFO
+    # slot, the slot's byte count, then the tail counter; the host plays the proxy (the reference's
+    # tests/public_api.cu:515-585). Forty slices wrap the four-slot FIFO ten times, so credits matter.
+    lib = _lib.load()
+    ok = ctypes.c_int()
+    _lib.check(lib.b2_selftest_direct_send(0, 40, ctypes.byref(ok)))
+    assert ok.value == 1
+    assert torch.ones(4, device="cuda").sum().item() == 4
