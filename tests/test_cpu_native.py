@@ -4,7 +4,7 @@ import pytest
 from conftest import run_native
 
 CPU_PROGRAMS = ["test_geometry", "test_validate", "test_bootstrap", "test_numa_topo", "test_socket_transport",
-                "test_rdma_proxy", "test_timeline", "test_net_edges", "test_mpi_adapter", "test_ll_sim", "test_ibverbs_backend"]
+                "test_rdma_proxy", "test_timeline", "test_net_edges", "test_mpi_adapter", "test_ll_sim", "test_pipe_sim", "test_ibverbs_backend"]
 
 
 @pytest.mark.parametrize("name", CPU_PROGRAMS)
