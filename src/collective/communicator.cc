@@ -952,7 +952,7 @@ void Communicator::Impl::launch_pipeline(const CollectiveArgs& args, const sched
         throw std::invalid_argument("all_reduce: the staging arena is too small for the tile pipeline (B200CCL_STAGING_BYTES)");
     const int slots = static_cast<int>(std::min<std::size_t>(4, staging_half_ / (static_cast<std::size_t>(cfg.grid) * tile)));
     cfg.nvls = plan.pipe_nvls && !loopback_ && stage_->multicast_ptr() != nullptr;
-    cfg.nvls_unroll = tuning_.nvls_unroll;
+    cfg.nvls_unroll = tuning_.pipeline_nvls_unroll;
     std::vector<dev::PipeArgs> per(local_.size());
     for (std::size_t i = 0; i < local_.size(); ++i) {
         dev::PipeArgs& a = per[i];

@@ -51,9 +51,14 @@ Tuning default_tuning() {
     //  * Tile pipeline for buffers peers cannot address against copy / barrier / reduce / barrier / copy:
     //    8 ranks 246 vs 224 us at 64 MiB, 835 vs 861 us at 256 MiB, 3142 vs 3414 us at 1 GiB; 2 ranks 152 vs 153 us
     //    at 64 MiB, 1711 vs 2271 us at 1 GiB.
+    //    4 ranks (switch reduce stage): 214 vs 236 us at 64 MiB, 710 vs 929 us at 256 MiB, 2494-2610 vs 3704 us at 1 GiB;
+    //    96 CTAs with one load in flight per thread: 479 / 568 / 646 GB/s at 64 MiB / 256 MiB / 1 GiB, 64 CTAs with two:
+    //    471 / 567 / 617, 128 CTAs with two: 480 / 575 / 615 (per-tile times double with the CTA count: the switch is the limit).
     t.pipeline_min_bytes = 128u << 20;
+    t.pipeline_min_bytes_upto4 = 64u << 20;
+    t.pipeline_nvls_unroll = 1;
     t.pipeline_tile_bytes = 256u << 10;
-    t.pipeline_max_ctas = 64;
+    t.pipeline_max_ctas = 96;
     t.pipeline_peer_max_ctas = 128;
     return t;
 }
@@ -104,7 +109,9 @@ Tuning tuning_from_text(const std::string& text, const Tuning& base, const std::
             if (as_int < 32 || as_int > 512 || as_int % 32 != 0) throw std::invalid_argument(where + "block_threads must be a multiple of 32 between 32 and 512");
             t.block_threads = as_int;
         }
-        else if (key == "pipeline_min_bytes") t.pipeline_min_bytes = bytes;
+        else if (key == "pipeline_min_bytes") t.pipeline_min_bytes = t.pipeline_min_bytes_upto4 = bytes;
+        else if (key == "pipeline_min_bytes_upto4") t.pipeline_min_bytes_upto4 = bytes;
+        else if (key == "pipeline_nvls_unroll") t.pipeline_nvls_unroll = std::max(as_int, 1);
         else if (key == "pipeline_tile_bytes") t.pipeline_tile_bytes = std::max<std::size_t>(bytes / 4096 * 4096, 32u << 10);
         else if (key == "pipeline_max_ctas") t.pipeline_max_ctas = std::max(as_int, 1);
         else if (key == "pipeline_peer_max_ctas") t.pipeline_peer_max_ctas = std::max(as_int, 1);
@@ -143,7 +150,9 @@ Tuning tuning_from_env() {
     t.block_threads = static_cast<int>(env::get_int("B200CCL_BLOCK_THREADS", t.block_threads, "NANO_NCCL_BLOCK_THREADS"));
     if (t.block_threads < 32 || t.block_threads > 512 || t.block_threads % 32 != 0)
         throw std::invalid_argument("B200CCL_BLOCK_THREADS must be a multiple of 32 between 32 and 512");
-    t.pipeline_min_bytes = env::get_bytes("B200CCL_PIPELINE_MIN_BYTES", t.pipeline_min_bytes);
+    if (env::get("B200CCL_PIPELINE_MIN_BYTES"))
+        t.pipeline_min_bytes = t.pipeline_min_bytes_upto4 = env::get_bytes("B200CCL_PIPELINE_MIN_BYTES", 0);
+    t.pipeline_nvls_unroll = std::max(1, static_cast<int>(env::get_int("B200CCL_PIPELINE_NVLS_UNROLL", t.pipeline_nvls_unroll)));
     t.pipeline_tile_bytes = std::max<std::size_t>(env::get_bytes("B200CCL_PIPELINE_TILE_BYTES", t.pipeline_tile_bytes) / 4096 * 4096, 32u << 10);
     t.pipeline_max_ctas = std::max(1, static_cast<int>(env::get_int("B200CCL_PIPELINE_MAX_CTAS", t.pipeline_max_ctas)));
     t.pipeline_peer_max_ctas = std::max(1, static_cast<int>(env::get_int("B200CCL_PIPELINE_PEER_MAX_CTAS", t.pipeline_peer_max_ctas)));
@@ -253,7 +262,8 @@ Plan make_plan(const CallShape& s, Algo forced, const Tuning& t) {
         p.error = "algo pipeline needs 16-byte aligned buffers and a message that is a multiple of 16 bytes";
         return p;
     }
-    if (forced == Algo::Pipeline || (forced == Algo::Auto && needs_staging && s.wide && bytes >= t.pipeline_min_bytes)) {
+    if (forced == Algo::Pipeline || (forced == Algo::Auto && needs_staging && s.wide &&
+                                     bytes >= (s.nranks <= 4 ? t.pipeline_min_bytes_upto4 : t.pipeline_min_bytes))) {
         p.algo = Algo::Pipeline;
         p.stage_in = p.stage_out = true;
         p.pipe_nvls = s.staging_multicast && s.nranks >= 3 && (s.redop == RedOp::Sum || s.redop == RedOp::Avg);

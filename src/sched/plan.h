@@ -73,8 +73,10 @@ struct Tuning {
     // below it: copy, barrier, reduce, barrier, copy). Every CTA gets the same number of tiles of about
     // pipeline_tile_bytes (never under 32 KiB); at most pipeline_max_ctas CTAs.
     std::size_t pipeline_min_bytes = 0;
+    std::size_t pipeline_min_bytes_upto4 = 0;  // the same threshold for up to four ranks (B200CCL_PIPELINE_MIN_BYTES sets both)
+    int pipeline_nvls_unroll = 1;              // multimem loads in flight per reducer thread (B200CCL_PIPELINE_NVLS_UNROLL)
     std::size_t pipeline_tile_bytes = 0;
-    int pipeline_max_ctas = 64;        // reduce stage through the switch (multimem)
+    int pipeline_max_ctas = 96;        // reduce stage through the switch (multimem)
     int pipeline_peer_max_ctas = 128;  // reduce stage over peer loads and stores
 };
 Tuning default_tuning();
@@ -84,7 +86,8 @@ Tuning tuning_from_env();
 // K/M/G suffixes. Keys: oneshot_max_bytes (all rank counts) or oneshot_max_bytes.<nranks>, nvls_min_bytes,
 // max_ctas, nvls_max_ctas, twoshot_max_ctas, nvls_unroll, bytes_per_cta, oneshot_bytes_per_cta, ll_max_bytes, ll_max_bytes_upto4,
 // wide32, block_threads,
-// pipeline_min_bytes, pipeline_tile_bytes, pipeline_max_ctas, pipeline_peer_max_ctas.
+// pipeline_min_bytes, pipeline_min_bytes_upto4, pipeline_tile_bytes, pipeline_max_ctas, pipeline_peer_max_ctas,
+// pipeline_nvls_unroll.
 // `python -m nano_nccl_b200.tuner --emit-tuning FILE` writes such a file from its measurements.
 // Throws std::invalid_argument naming the file and line on an unknown key or a bad value.
 Tuning tuning_from_text(const std::string& text, const Tuning& base, const std::string& origin);
