@@ -95,7 +95,9 @@ def link_bytes_per_direction(algo, nbytes, n):
     """Bytes that leave (and that enter) one GPU over NVLink for an AllReduce of nbytes per rank."""
     if n < 2:
         return 0.0
-    if algo in ("nvls",):            # every shard goes out once to the switch and the result comes back multicast
+    if algo == "nvls" or (algo == "pipeline" and n >= 3):
+        # every shard goes out once to the switch and the result comes back multicast (the tile pipeline
+        # reduces through the switch from three ranks up; its staging copies stay inside the GPU)
         return nbytes * (1 + 1.0 / n)
     if algo in ("twoshot", "ring"):  # pull the own shard from n-1 peers, push the result to n-1 peers
         return nbytes * 2.0 * (n - 1) / n
