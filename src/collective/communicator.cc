@@ -202,9 +202,8 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
     staging_half_ = config.staging_bytes > 0 ? config.staging_bytes / 2
                                              : env::get_bytes("B200CCL_STAGING_BYTES", std::size_t(256) << 20) / 2;
     staging_half_ = std::max<std::size_t>(staging_half_ / 4096 * 4096, 4096);
-    channels_ = config.channels > 0 ? config.channels
-                                    : static_cast<int>(env::get_int("B200CCL_NCHANNELS", kDefaultChannels, "NANO_NCCL_NCHANNELS"));
-    channels_ = std::max(1, std::min(channels_, kMaxChannels));
+    // 0: decided below, once the transport is known.
+    channels_ = config.channels > 0 ? config.channels : static_cast<int>(env::get_int("B200CCL_NCHANNELS", 0, "NANO_NCCL_NCHANNELS"));
     tuning_ = sched::tuning_from_env();
     if (config.max_ctas > 0) {  // an explicit cap applies to every algorithm
         tuning_.max_ctas = tuning_.nvls_max_ctas = tuning_.twoshot_max_ctas = std::min(config.max_ctas, dev::kMaxCtas);
@@ -245,6 +244,16 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
 
     topo_ = topo::discover(config.devices);
     resolve_transport();
+    if (channels_ <= 0) {
+        // One ring CTA moves about 8 GB/s over NVLink, so peer-memory rings want many channels (8 GPUs, 64 MiB:
+        // 272 GB/s with 32, 193 with 16); host-memory edges are limited by the host path and do best with few
+        // (8 GPUs: 11.7 GB/s with 4, 10.3 with 8, 9.2 with 16); network edges keep a proxy thread pair per channel.
+        channels_ = resolved_ == TransportKind::P2p ? 32
+                    : (resolved_ == TransportKind::Shm || resolved_ == TransportKind::Mixed) ? 4 : kDefaultChannels;
+        // Emulated ranks share one GPU and one cooperative launch: all their channel CTAs must be resident at once.
+        if (loopback_) channels_ = std::min(channels_, std::max(1, 64 / nranks_));
+    }
+    channels_ = std::max(1, std::min(channels_, kMaxChannels));
     {
         // Per-edge view of the ring: edges inside a process use peer memory or host memory, decided
         // edge by edge; edges between processes use exported peer memory unless a network transport
