@@ -206,7 +206,8 @@ Communicator::Impl::Impl(const CommunicatorConfig& config, Bootstrap* bootstrap)
     channels_ = config.channels > 0 ? config.channels : static_cast<int>(env::get_int("B200CCL_NCHANNELS", 0, "NANO_NCCL_NCHANNELS"));
     tuning_ = sched::tuning_from_env();
     if (config.max_ctas > 0) {  // an explicit cap applies to every algorithm
-        tuning_.max_ctas = tuning_.nvls_max_ctas = tuning_.twoshot_max_ctas = std::min(config.max_ctas, dev::kMaxCtas);
+        tuning_.max_ctas = tuning_.nvls_max_ctas = tuning_.nvls_staged_max_ctas = tuning_.twoshot_max_ctas =
+            std::min(config.max_ctas, dev::kMaxCtas);
     }
 
     // Rank layout: ranks are contiguous per process, in bootstrap order

@@ -51,6 +51,7 @@ struct Tuning {
     std::size_t nvls_min_bytes = 0;                // NVLS from this size up (when available)
     int max_ctas = 128;                            // hard cap for every algorithm (B200CCL_MAX_CTAS)
     int nvls_max_ctas = 64;                        // more CTAs than this slowed the multimem kernels down
+    int nvls_staged_max_ctas = 64;                 // when the same CTAs also copy the message in and out of the arena
     int twoshot_max_ctas = 128;
     int nvls_unroll = 2;                           // multimem loads in flight per thread (B200CCL_NVLS_UNROLL)
     std::size_t bytes_per_cta = 0;                 // work given to one CTA before another is added
